@@ -1,7 +1,7 @@
 """The cache manager: pages with a block table per request, in groups, and state slots.
 
 A *group* is a set of layers with the same need: ("paged", None) keeps every key,
-("paged", W) keeps a window of W positions.  Each group has pages of its own (its own pool of
+("paged", W) keeps a window of W positions, ("paged", -C) the positions of the current block of C.  Each group has pages of its own (its own pool of
 page ids and, per layer of the group, device tensors of its own in the layout its spec chooses:
 [pages, 2, kv heads, page_size, head_dim] for keys and values of one width) and each request has
 one block table per group: entry i is the page that holds
@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 import torch
 
 from ..errors import CapacityError
-from ..parts.spec import PagedKVSpec, SlotStateSpec
+from ..parts.spec import PagedKVSpec, SlotStateSpec, first_reachable
 from .pages import PagePool, StateSlots
 
 
@@ -74,7 +74,7 @@ class CacheManager:
         for idx, entry in self.specs.items():
             for spec in _as_tuple(entry):
                 if isinstance(spec, PagedKVSpec):
-                    key = ("paged", spec.window)
+                    key = ("paged", spec.reach)
                     if key not in self.groups:
                         n = num_pages[key] if isinstance(num_pages, dict) else num_pages
                         self.groups[key] = PagePool(int(n))
@@ -94,7 +94,7 @@ class CacheManager:
             made = []
             for spec in _as_tuple(entry):
                 if isinstance(spec, PagedKVSpec):
-                    n = max(self.groups[("paged", spec.window)].total, 1)
+                    n = max(self.groups[("paged", spec.reach)].total, 1)
                     dtype = _CACHE_DTYPES[spec.cache_dtype] if spec.cache_dtype else self.dtype
                     made.append(tuple(torch.zeros(shape, dtype=dtype, device=self.device)
                                       for shape in spec.pool_shapes(n, self.page_size)))
@@ -131,7 +131,7 @@ class CacheManager:
         for entry in cache_specs.values():
             for spec in _as_tuple(entry):
                 if isinstance(spec, PagedKVSpec):
-                    key = ("paged", spec.window)
+                    key = ("paged", spec.reach)
                     esz = torch.empty((), dtype=_CACHE_DTYPES[spec.cache_dtype] if spec.cache_dtype
                                       else dtype).element_size()
                     out[key] = out.get(key, 0) + spec.elements_per_page(page_size) * esz
@@ -147,10 +147,7 @@ class CacheManager:
 
     def _first_needed_page(self, key, from_token: int) -> int:
         """First table entry that a query at position >= from_token can still reach."""
-        window = key[1]
-        if window is None:
-            return 0
-        return max(0, from_token - window + 1) // self.page_size
+        return first_reachable(key[1], from_token) // self.page_size
 
     def missing_pages(self, rc: RequestCache, total_tokens: int) -> dict:
         """{group key -> pages still to take} so that positions [num_tokens, total_tokens) fit."""
@@ -243,7 +240,7 @@ class CacheManager:
         views = []
         for spec, tensors in zip(_as_tuple(entry), self._tensors[idx]):
             if isinstance(spec, PagedKVSpec):
-                views.append(PagedView(tensors[0], block_tables[("paged", spec.window)], self.page_size, tensors))
+                views.append(PagedView(tensors[0], block_tables[("paged", spec.reach)], self.page_size, tensors))
             else:
                 views.append(SlotView(list(tensors)))
         return tuple(views) if isinstance(entry, (tuple, list)) else views[0]

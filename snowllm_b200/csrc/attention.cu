@@ -229,7 +229,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   __shared__ float s_mx, s_inv;
   const int m = row_list ? row_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int pos = positions[m];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = first_key(pos, window);
   const int n = pos / chunk - lo / chunk + 1;              // chunks this row really has
   const size_t base = ((size_t)blockIdx.x * nh + head) * num_chunks;
   if (threadIdx.x < 32) {

@@ -6,6 +6,9 @@
 //     head (h, map) reads the key at offset map*dk of kv head h / group, and every map has an output row
 //     of its own [M, nq, dv] (a mixer that subtracts one map from another does so afterwards);
 //   * a bias per (query head, distance): s = (q . k) * scale + bias[head][min(i - j, bias_len - 1)];
+//   * `window` > 0: the last `window` keys; < 0: the keys of the query's own block of -window positions
+//     (blocks counted from position 0); a factor per query head on the scale; a sink per query head (one
+//     more term exp(sink) in the softmax's sum, without a key or a value);
 //   * scores, softmax weights and the products with the values in float whatever the cache dtype (the
 //     weights are never rounded to 16 bits), output in float or in the compute dtype.
 //
@@ -56,6 +59,7 @@ template <int N> __device__ __forceinline__ void sa_cp_async_wait() {
 // column q_off ([nq, dk]), k at k_off ([nkh, dk], nkh = kv heads * maps) and v at v_off ([nkv, dv]).
 template <typename T>
 __global__ void split_prepare_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
+                                     const float* __restrict__ proj_bias,
                                      SmallVec q_gamma, SmallVec k_gamma, int has_norm, float eps,
                                      const float* __restrict__ inv_freq, int rot_dim, float rot_mult,
                                      const int* __restrict__ positions, const int* __restrict__ row_seg,
@@ -77,16 +81,22 @@ __global__ void split_prepare_kernel(const T* __restrict__ proj, long long ld, i
     const int h = unit - nq - nkh;
     const T* src = row + v_off + (size_t)h * dv;
     T* dst = vpool + (((size_t)page * nkv + h) * page_size + pos % page_size) * dv;
-    for (int d = lane; d < dv; d += 32) dst[d] = src[d];
+    if (proj_bias) {
+      const float* bs = proj_bias + v_off + (size_t)h * dv;
+      for (int d = lane; d < dv; d += 32) dst[d] = from_f<T>(to_f<T>(src[d]) + bs[d]);
+    } else {
+      for (int d = lane; d < dv; d += 32) dst[d] = src[d];
+    }
     return;
   }
   const bool is_q = unit < nq;
   const int h = is_q ? unit : unit - nq;
   const T* src = row + (is_q ? q_off : k_off) + (size_t)h * dk;
   float* xs = sp_sh + (size_t)warp * dk;
+  const float* bs = proj_bias ? proj_bias + (is_q ? q_off : k_off) + (size_t)h * dk : nullptr;
   float ss = 0.f;
   for (int d = lane; d < dk; d += 32) {
-    const float v = to_f<T>(src[d]);
+    const float v = to_f<T>(src[d]) + (bs ? bs[d] : 0.f);
     xs[d] = v;
     ss = fmaf(v, v, ss);
   }
@@ -94,7 +104,11 @@ __global__ void split_prepare_kernel(const T* __restrict__ proj, long long ld, i
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / (float)dk + eps);
     const SmallVec& g = is_q ? q_gamma : k_gamma;
-    for (int d = lane; d < dk; d += 32) xs[d] = xs[d] * inv * g[d];
+    if (g.p) {
+      for (int d = lane; d < dk; d += 32) xs[d] = xs[d] * inv * g[d];
+    } else {                                           // a norm without a weight
+      for (int d = lane; d < dk; d += 32) xs[d] = xs[d] * inv;
+    }
   }
   __syncwarp();
   T* dst;
@@ -120,7 +134,8 @@ __global__ void split_prepare_kernel(const T* __restrict__ proj, long long ld, i
   }
 }
 
-SNK_API int snk_split_prepare(const void* proj, long long ld, int q_off, int k_off, int v_off, const void* q_gamma,
+SNK_API int snk_split_prepare(const void* proj, long long ld, int q_off, int k_off, int v_off,
+                              const float* proj_bias, const void* q_gamma,
                               const void* k_gamma, int gamma_f32, int has_norm, float eps, const float* inv_freq,
                               int rot_dim, float rot_mult, const int* positions, const int* row_seg,
                               const int* block_table, int max_pages, int page_size, void* kpool, void* vpool,
@@ -135,7 +150,7 @@ SNK_API int snk_split_prepare(const void* proj, long long ld, int q_off, int k_o
   const size_t smem = (size_t)warps * dk * sizeof(float);
   if (smem > 48 * 1024) return SNK_ERR_SIZE;
   SNK_DISPATCH(dtype, snk_launch(split_prepare_kernel<T>, dim3(grid), dim3(warps * 32), smem, stream,
-                                 static_cast<const T*>(proj), ld, q_off, k_off, v_off,
+                                 static_cast<const T*>(proj), ld, q_off, k_off, v_off, proj_bias,
                                  SmallVec{q_gamma, gamma_f32}, SmallVec{k_gamma, gamma_f32}, has_norm, eps, inv_freq,
                                  rot_dim, rot_mult, positions, row_seg, block_table, max_pages, page_size,
                                  static_cast<T*>(kpool), static_cast<T*>(vpool), static_cast<T*>(q_out), nq, nkh,
@@ -152,7 +167,8 @@ __global__ void split_attention_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, void* __restrict__ out, int out_f32,
     int nq, int nkv, int maps, int dk, int dv, int window, float scale, const float* __restrict__ bias,
-    int bias_len, int vec_ok, int chunk, int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    int bias_len, const float* __restrict__ head_scale, const float* __restrict__ sink, int vec_ok, int chunk,
+    int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
   constexpr int VEC = SaVec<T>::N;
@@ -163,7 +179,7 @@ __global__ void split_attention_kernel(
   const int hpv = nq / nkv;                              // query heads (maps counted) per kv head
   const int units = rows * hpv;
   const int pos0 = positions[m0];
-  int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int lo = first_key(pos0, window);
   int hi = pos0 + rows - 1;                              // the last row's own position
   if (num_chunks > 1) {
     // single rows with their keys cut into chunks aligned to absolute positions: this block takes one
@@ -183,7 +199,8 @@ __global__ void split_attention_kernel(
   for (int i = threadIdx.x; i < units * dk; i += blockDim.x) {
     const int u = i / dk, d = i - u * dk;
     const int r = u / hpv, hh = u - r * hpv;
-    qs[i] = to_f<T>(q[((size_t)(m0 + r) * nq + kvh * hpv + hh) * dk + d]) * scale;
+    const float hs = head_scale ? scale * head_scale[kvh * hpv + hh] : scale;
+    qs[i] = to_f<T>(q[((size_t)(m0 + r) * nq + kvh * hpv + hh) * dk + d]) * hs;
   }
   const int* bt = block_table + (size_t)row_seg[m0] * max_pages;
   const int t_first = (lo / SA_TILE) * SA_TILE;
@@ -226,11 +243,19 @@ __global__ void split_attention_kernel(
     sa_cp_async_commit();
   };
 
+  // a sink is one more term exp(sink) of the row's sum that has no key: the block that holds the row's
+  // first keys starts from (maximum = sink, sum = 1)
+  const bool sink_here = sink != nullptr && (num_chunks <= 1 || blockIdx.z == 0);
   float mx[UPW], l[UPW], o[UPW][DPL];
 #pragma unroll
   for (int i = 0; i < UPW; ++i) {
+    const int u0 = warp + nwarps * i;
     mx[i] = -INFINITY;
     l[i] = 0.f;
+    if (sink_here && u0 < units) {
+      mx[i] = sink[kvh * hpv + u0 % hpv];
+      l[i] = 1.f;
+    }
 #pragma unroll
     for (int e = 0; e < DPL; ++e) o[i][e] = 0.f;
   }
@@ -252,7 +277,7 @@ __global__ void split_attention_kernel(
       const int r = u / hpv, hh = u - r * hpv;
       const int map = hh % maps;
       const int p = pos0 + r;
-      const int klo = max(lo, window > 0 ? p - window + 1 : 0);
+      const int klo = max(lo, first_key(p, window));
       const int khi = min(p, hi);
       if (t0 > khi || t0 + SA_TILE - 1 < klo) continue;  // none of this unit's keys in the tile
       const bool valid = kp >= klo && kp <= khi;
@@ -373,7 +398,8 @@ __global__ void split_attention_mma_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, void* __restrict__ out, int out_f32,
     int nq, int nkv, int maps, int dk, int dv, int window, float scale, const float* __restrict__ bias,
-    int bias_len, int chunk, int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    int bias_len, const float* __restrict__ head_scale, const float* __restrict__ sink, int chunk, int num_chunks,
+    float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -382,7 +408,7 @@ __global__ void split_attention_mma_kernel(
   const int kvh = blockIdx.y;
   const int hpv = nq / nkv, G = hpv / maps;
   const int pos0 = positions[m0];
-  int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int lo = first_key(pos0, window);
   int hi = pos0 + rows - 1;
   if (num_chunks > 1) {
     const int cnk = lo / chunk + (int)blockIdx.z;
@@ -473,6 +499,15 @@ __global__ void split_attention_mma_kernel(
   };
 
   float mx[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float scale2h[2];
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    scale2h[h2] = head_scale ? scale2 * head_scale[head[h2]] : scale2;
+    if (sink != nullptr && live[h2] && (num_chunks <= 1 || blockIdx.z == 0)) {   // the sink: a term without a key
+      mx[h2] = sink[head[h2]] * 1.4426950408889634f;
+      l[h2] = 1.f;
+    }
+  }
   float o[DVT][4];
 #pragma unroll
   for (int nt = 0; nt < DVT; ++nt)
@@ -481,7 +516,7 @@ __global__ void split_attention_mma_kernel(
   int klo[2], khi[2];
 #pragma unroll
   for (int h2 = 0; h2 < 2; ++h2) {
-    klo[h2] = max(lo, window > 0 ? p_row[h2] - window + 1 : 0);
+    klo[h2] = max(lo, first_key(p_row[h2], window));
     khi[h2] = live[h2] ? min(p_row[h2], hi) : -1;           // a slot nobody owns sees no key
   }
 
@@ -497,7 +532,7 @@ __global__ void split_attention_mma_kernel(
     {
       const int s_lo = (warp / maps) * 16, s_hi = min(slots - 1, s_lo + 15);
       const int p_lo = pos0 + s_lo / G, p_hi = pos0 + s_hi / G;
-      const int w_lo = max(lo, window > 0 ? p_lo - window + 1 : 0), w_hi = min(p_hi, hi);
+      const int w_lo = max(lo, first_key(p_lo, window)), w_hi = min(p_hi, hi);
       if (t0 > w_hi || t0 + SA_TILE - 1 < w_lo) continue;
     }
     const unsigned char* ks_ = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
@@ -531,7 +566,7 @@ __global__ void split_attention_mma_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int h2 = e >> 1;
-          float s = sc[nt][e] * scale2;
+          float s = sc[nt][e] * scale2h[h2];
           if (bias) {
             const int dist = p_row[h2] - (t0 + nt * 8 + tq * 2 + (e & 1));
             s = fmaf(brow[h2][min(dist, bias_len - 1)], 1.4426950408889634f, s);
@@ -547,7 +582,7 @@ __global__ void split_attention_mma_kernel(
         for (int e = 0; e < 4; ++e) {
           const int h2 = e >> 1;
           const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
-          float s = sc[nt][e] * scale2;
+          float s = sc[nt][e] * scale2h[h2];
           const bool valid = kp >= klo[h2] && kp <= khi[h2];
           if (bias && valid)
             s = fmaf(bias[(size_t)head[h2] * bias_len + min(p_row[h2] - kp, bias_len - 1)], 1.4426950408889634f, s);
@@ -674,7 +709,8 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
                         const int* __restrict__ block_table, int max_pages, int page_size,
                         const int* __restrict__ positions, const int* __restrict__ row_seg,
                         void* __restrict__ out, int out_f32, int nq, int nkv, int maps, int dk, int dv, int window,
-                        float scale, const float* __restrict__ bias, int bias_len, int num_chunks,
+                        float scale, const float* __restrict__ bias, int bias_len,
+                        const float* __restrict__ head_scale, const float* __restrict__ sink, int num_chunks,
                         float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
@@ -683,7 +719,7 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
   const int m = blockIdx.x, kvh = blockIdx.y;
   const int hpv = nq / nkv, G = hpv / maps;
   const int pos = positions[m];
-  const int lo_row = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo_row = first_key(pos, window);
   const int cnk = lo_row / SD_CHUNK + (int)blockIdx.z;
   if ((long long)cnk * SD_CHUNK > pos) return;
   const int c0 = cnk * SD_CHUNK;
@@ -772,7 +808,7 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
         for (int e = 0; e < 4; ++e) {
           const int h2 = e >> 1;
           const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
-          float sv = sc[nt][e] * scale2;
+          float sv = sc[nt][e] * (head_scale ? scale2 * head_scale[head[h2]] : scale2);
           const bool valid = live[h2] && kp >= lo && kp <= hi;
           if (bias && valid)
             sv = fmaf(bias[(size_t)head[h2] * bias_len + min(pos - kp, bias_len - 1)], 1.4426950408889634f, sv);
@@ -855,10 +891,16 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
   for (int i = threadIdx.x; i < hpv * dv; i += blockDim.x) {
     const int mg = i / dv, d = i - mg * dv;              // mg = map * G + head of the kv head
     const float* r = red + (size_t)mg * SD_WARPS * red_stride;
+    const int head = kvh * hpv + (mg % G) * maps + mg / G;
     float mx = -INFINITY;
 #pragma unroll
     for (int w = 0; w < SD_WARPS; ++w) mx = fmaxf(mx, r[w * red_stride + dv]);
     float l = 0.f, acc = 0.f;
+    if (sink != nullptr && blockIdx.z == 0) {            // the sink: one more term of the sum, without a key
+      const float sk = sink[head] * 1.4426950408889634f;
+      mx = fmaxf(mx, sk);
+      l = exp2f(sk - mx);
+    }
 #pragma unroll
     for (int w = 0; w < SD_WARPS; ++w) {
       const float mw = r[w * red_stride + dv];
@@ -866,7 +908,6 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
       l = fmaf(r[w * red_stride + dv + 1], f, l);
       acc = fmaf(r[w * red_stride + d], f, acc);
     }
-    const int head = kvh * hpv + (mg % G) * maps + mg / G;
     if (num_chunks > 1) {
       const size_t slot = ((size_t)m * nq + head) * num_chunks + blockIdx.z;
       part_o[slot * dv + d] = acc;
@@ -924,8 +965,8 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
                                 int max_pages, int page_size, const int* positions, const int* row_seg,
                                 const int* tiles, int num_tiles, int tile_rows, void* out, int out_f32, int nq,
                                 int nkv, int maps, int dk, int dv, int window, float scale, const float* bias,
-                                int bias_len, int chunk, int num_chunks, void* scratch, int dtype,
-                                cudaStream_t stream) {
+                                int bias_len, const float* head_scale, const float* sink, int chunk,
+                                int num_chunks, void* scratch, int dtype, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nkv <= 0 || maps <= 0 || nq % (nkv * maps) || dk <= 0 || dv <= 0 || dv > 256) return SNK_ERR_SIZE;
   const int hpv = nq / nkv;
@@ -951,7 +992,7 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_decode_mma_kernel<DKS_, DVT_>, dim3(grid), dim3(SD_WARPS * 32), smem, stream,           \
                static_cast<const bf16*>(q), static_cast<const bf16*>(kpool), static_cast<const bf16*>(vpool), \
                block_table, max_pages, page_size, positions, row_seg, out, out_f32, nq, nkv, maps, dk, dv,   \
-               window, scale, bias, bias_len, num_chunks, part_o, part_ml);                                  \
+               window, scale, bias, bias_len, head_scale, sink, num_chunks, part_o, part_ml);                                  \
   } while (0)
     if (dk <= 64 && dv <= 64) SD_MMA(4, 8);
     else if (dk <= 64) SD_MMA(4, 16);
@@ -979,7 +1020,7 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_attention_mma_kernel<DKS_, DVT_>, dim3(grid), dim3(warps * 32), smem, stream,           \
                static_cast<const bf16*>(q), static_cast<const bf16*>(kpool), static_cast<const bf16*>(vpool), \
                block_table, max_pages, page_size, positions, row_seg, tiles, out, out_f32, nq, nkv, maps,    \
-               dk, dv, window, scale, bias, bias_len, chunk, num_chunks, part_o, part_ml);                   \
+               dk, dv, window, scale, bias, bias_len, head_scale, sink, chunk, num_chunks, part_o, part_ml);                   \
   } while (0)
     if (dk <= 64 && dv <= 64) SA_MMA(4, 8);
     else if (dk <= 64) SA_MMA(4, 16);
@@ -1009,7 +1050,8 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_attention_kernel<T, DPL_, UPW_>, dim3(grid), dim3(warps * 32), smem, stream,      \
                static_cast<const T*>(q), static_cast<const T*>(kpool), static_cast<const T*>(vpool),   \
                block_table, max_pages, page_size, positions, row_seg, tiles, out, out_f32, nq, nkv,    \
-               maps, dk, dv, window, scale, bias, bias_len, vec_ok, chunk, num_chunks, part_o, part_ml); \
+               maps, dk, dv, window, scale, bias, bias_len, head_scale, sink, vec_ok, chunk, num_chunks,  \
+               part_o, part_ml);                                                                        \
   } while (0)
 #define SA_LAUNCH_U(DPL_)                  \
   do {                                     \

@@ -67,6 +67,14 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float
                                             *reinterpret_cast<const uint32_t*>(&hi));
 }
 
+// The first key that a query at position `pos` reaches, by the `window` argument the attention kernels
+// share: W > 0 the last W keys (a sliding window, the query's own position included); -C < 0 the keys of the
+// query's own block of C positions (blocks counted from position 0 of the sequence); 0 every earlier key.
+__host__ __device__ __forceinline__ int first_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos - pos % (-window);
+  return 0;
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

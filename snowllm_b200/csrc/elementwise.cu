@@ -1,6 +1,6 @@
 // Embedding gather, fused residual-add + RMSNorm, SwiGLU activation.
 //
-// Embedding: h[m,:] = E[ids[m],:]                      (snowllm/ops/embedding.py:12-25)
+// Embedding: h[m,:] = E[ids[m],:] * scale              (snowllm/ops/embedding.py:12-25)
 // RMSNorm:   y = x * rsqrt(mean(x^2) + eps) * weight    (snowllm/ops/norm.py:11-30)
 // SwiGLU:    out = silu(gate) * up                      (snowllm/ops/mlp.py:12-20)
 // Both are evaluated in float and rounded to the compute dtype once, at the store (SnowLLM's
@@ -14,7 +14,7 @@
 // has not read yet (the step that follows a sampled token can then be launched before the token is known).
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ pending, int num_pending,
-                                 const T* __restrict__ table, float* __restrict__ out, int H, int V) {
+                                 const T* __restrict__ table, float* __restrict__ out, int H, int V, float scale) {
   pdl_begin();
   const int m = blockIdx.x;
   int id = ids[m];
@@ -22,15 +22,15 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
   const bool ok = id >= 0 && id < V;     // the host checks ids; a bad one reads nothing
   const T* row = table + (size_t)(ok ? id : 0) * H;
   float* o = out + (size_t)m * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f<T>(row[i]) : 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f<T>(row[i]) * scale : 0.f;
 }
 
 SNK_API int snk_embedding(const int* ids, const int* pending, int num_pending, const void* table, float* out,
-                          int M, int H, int V, int dtype, cudaStream_t stream) {
+                          int M, int H, int V, int dtype, float scale, cudaStream_t stream) {
   if (M <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   SNK_DISPATCH(dtype, snk_launch(embedding_kernel<T>, dim3(M), dim3(threads), 0, stream,
-                          ids, pending, num_pending, static_cast<const T*>(table), out, H, V));
+                          ids, pending, num_pending, static_cast<const T*>(table), out, H, V, scale));
   SNK_LAUNCH_CHECK();
   return 0;
 }

@@ -1,4 +1,5 @@
-// Routed feed-forward: sigmoid router with top-k, token -> expert sort, weighted combine.
+// Routed feed-forward: router (a sigmoid per expert, or a softmax over all) with top-k, token -> expert sort,
+// weighted combine.
 //
 //   logits = u_f32 . Wr^T (float);  p = sigmoid(logits);  the k largest of p + bias select
 //   (the bias only selects; equal scores go to the lower expert index);  w = p[sel];
@@ -18,8 +19,28 @@
 
 // The k largest of score[] (ties to the lower index, NaN never wins) by one warp; weights from prob[],
 // normalised by (sum + 1e-6) when asked, times the scaling factor.  score[] is consumed.
+// norm_topk is a pair of flags: bit 0 renormalises the picks' weights by their sum; bit 1 says that prob[] and
+// score[] hold the experts' LOGITS and the weights are their softmax over all E experts (exp(z - max) over
+// the sum of all, in float).  The order of the logits is the order of the softmax, ties included.
+#define ROUTE_RENORM 1
+#define ROUTE_SOFTMAX 2
+__device__ __forceinline__ float route_score(float logit, int flags) {
+  return (flags & ROUTE_SOFTMAX) ? logit : 1.f / (1.f + expf(-logit));
+}
 __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids, float* wts, int E, int k,
-                                            int norm_topk, float scaling, int lane) {
+                                            int flags, float scaling, int lane) {
+  const int norm_topk = flags & ROUTE_RENORM;
+  if (flags & ROUTE_SOFTMAX) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) den += expf(prob[e] - mx);
+    den = warp_sum(den);
+    const float inv = 1.f / den;
+    for (int e = lane; e < E; e += 32) prob[e] = expf(prob[e] - mx) * inv;
+    __syncwarp();
+  }
   float wsum = 0.f;
   float my_w = 0.f;              // lane j keeps the weight of pick j (k <= 32 per round)
   int my_id = 0;
@@ -124,7 +145,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const flo
         ? warp_dot<T, float>(xr, static_cast<const float*>(wr.p) + (size_t)e * H, H, lane, vec)
         : warp_dot<T, bf16>(xr, static_cast<const bf16*>(wr.p) + (size_t)e * H, H, lane, vec);
     if (lane == 0) {
-      const float p = 1.f / (1.f + expf(-acc));
+      const float p = route_score(acc, norm_topk);
       prob[e] = p;
       score[e] = bias ? p + bias[e] : p;
     }
@@ -172,7 +193,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* _
       x += 0.f;                                          // the sum starts from zero, as the product's own sum does
       for (int q = 1; q < planes; ++q) x += logits[(size_t)q * M * E + (size_t)m * E + e];
     }
-    const float p = 1.f / (1.f + expf(-x));
+    const float p = route_score(x, norm_topk);
     prob[e] = p;
     score[e] = bias ? p + bias[e] : p;
   }
@@ -310,7 +331,7 @@ __global__ void moe_topk_sort_kernel(const float* __restrict__ logits, const flo
   float* score = prob + E;
   for (int m = warp; m < M; m += nwarp) {
     for (int e = lane; e < E; e += 32) {
-      const float p = 1.f / (1.f + expf(-logits[(size_t)m * E + e]));
+      const float p = route_score(logits[(size_t)m * E + e], norm_topk);
       prob[e] = p;
       score[e] = bias ? p + bias[e] : p;
     }
@@ -502,7 +523,7 @@ norm_route_sort_kernel(float* __restrict__ residual, const float* __restrict__ d
           ? warp_dot_shared<float, false>(xs, static_cast<const float*>(wr.p) + (size_t)e * H, H, lane, vec)
           : warp_dot_shared<bf16, false>(xs, static_cast<const bf16*>(wr.p) + (size_t)e * H, H, lane, vec);
     if (lane == 0) {
-      const float p = 1.f / (1.f + expf(-acc));
+      const float p = route_score(acc, norm_topk);
       prob[e] = p;
       score[e] = bias ? p + bias[e] : p;
     }

@@ -10,7 +10,7 @@
 //                    still in pieces), then the Dynamic Tanh norm tanh(alpha * x) * w + b of the sum: a norm
 //                    without mean or variance
 //   head_norm_gate:  per (row, head): o = a (- lambda * b), o / sqrt(mean(o^2) + eps) (* w) * mult
-//                    * sigmoid(g): the end of a mixer whose heads are normalised one by one and gated
+//                    * sigmoid(g) (or * silu(g)): the end of a mixer whose heads are normalised one by one and gated
 //
 // All statistics, sums and gates are evaluated in float; values are rounded to the compute dtype once,
 // at the store.
@@ -93,9 +93,12 @@ SNK_API int snk_cast_rows(const float* x, void* out, long long n, int dtype, cud
 // ---------------------------------------------------------------------------------------------
 // Columns of gate_up: (gate | up), or with `interleaved` blocks of 8 gate columns followed by the 8 up
 // columns of the same features.
+// act ACT_SWISH_CLAMP (the gated kind only): g = min(g, limit), u = clamp(u, -limit, limit), and the product is
+// g * sigmoid(1.702 g) * (u + 1).
+#define ACT_SWISH_CLAMP 4
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int M, int inter,
-                                 int interleaved, int act) {
+                                 int interleaved, int act, float limit) {
   pdl_begin();
   const long long n = (long long)M * inter;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -112,18 +115,26 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
       g = to_f<T>(row[c]);
       u = to_f<T>(row[inter + c]);
     }
-    out[i] = from_f<T>(act_apply(g, act) * u);
+    if (act == ACT_SWISH_CLAMP) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      out[i] = from_f<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+    } else {
+      out[i] = from_f<T>(act_apply(g, act) * u);
+    }
   }
 }
 
-SNK_API int snk_gated_act(const void* gate_up, void* out, int M, int inter, int interleaved, int act, int dtype,
-                          cudaStream_t stream) {
+SNK_API int snk_gated_act(const void* gate_up, void* out, int M, int inter, int interleaved, int act, float limit,
+                          int dtype, cudaStream_t stream) {
   if (M <= 0 || inter <= 0) return 0;
-  if (act < 0 || act > ACT_RELU2 || (interleaved && inter % 8)) return SNK_ERR_SIZE;
+  if (act < 0 || act > ACT_SWISH_CLAMP || (interleaved && inter % 8)) return SNK_ERR_SIZE;
+  if (act == ACT_SWISH_CLAMP && !(limit > 0.f)) return SNK_ERR_SIZE;
   const long long n = (long long)M * inter;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   SNK_DISPATCH(dtype, snk_launch(gated_act_kernel<T>, dim3(blocks), dim3(256), 0, stream,
-                                 static_cast<const T*>(gate_up), static_cast<T*>(out), M, inter, interleaved, act));
+                                 static_cast<const T*>(gate_up), static_cast<T*>(out), M, inter, interleaved, act,
+                                 limit));
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -136,7 +147,8 @@ SNK_API int snk_gated_act(const void* gate_up, void* out, int M, int inter, int 
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ a, int a_stride, int second, float lambda,
                                       SmallVec w, int has_w, SmallVec g, int has_g, long long g_ld,
-                                      T* __restrict__ out, int M, int heads, int dv, float eps, float mult) {
+                                      T* __restrict__ out, int M, int heads, int dv, float eps, float mult,
+                                      int gate_silu) {
   pdl_begin();
   const int lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -158,14 +170,17 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ a, int a_stride,
     const int col = h * dv + c;
     o *= inv;
     if (has_w) o *= w[col];
-    if (has_g) o *= sigmoid_f(g[(size_t)(m * g_ld + col)]);
+    if (has_g) {
+      const float z = g[(size_t)(m * g_ld + col)];
+      o *= gate_silu ? z * sigmoid_f(z) : sigmoid_f(z);
+    }
     out[m * (long long)heads * dv + col] = from_f<T>(o);
   }
 }
 
 SNK_API int snk_head_norm_gate(const float* a, int a_stride, int second, float lambda, const void* w, int w_f32,
                                const void* g, int g_f32, long long g_ld, void* out, int M, int heads, int dv, float eps,
-                               float mult, int dtype, cudaStream_t stream) {
+                               float mult, int gate_silu, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (heads <= 0 || dv <= 0 || a_stride < dv + second) return SNK_ERR_SIZE;
   const long long units = (long long)M * heads;
@@ -174,7 +189,8 @@ SNK_API int snk_head_norm_gate(const float* a, int a_stride, int second, float l
   if (blocks > 0x7fffffffLL) return SNK_ERR_SIZE;
   SNK_DISPATCH(dtype, snk_launch(head_norm_gate_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
                                  a, a_stride, second, lambda, SmallVec{w, w_f32}, (int)(w != nullptr),
-                                 SmallVec{g, g_f32}, (int)(g != nullptr), g_ld, static_cast<T*>(out), M, heads, dv, eps, mult));
+                                 SmallVec{g, g_f32}, (int)(g != nullptr), g_ld, static_cast<T*>(out), M, heads, dv, eps, mult,
+                                 gate_silu));
   SNK_LAUNCH_CHECK();
   return 0;
 }

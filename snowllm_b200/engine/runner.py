@@ -16,6 +16,7 @@ from ..cache import CacheManager, RequestCache
 from ..config.engine import DEFAULT_MAX_GRAPHS, MAX_NUM_SEQS
 from ..errors import CapacityError, KernelError, SnowLLMError
 from ..ops import kernels
+from ..parts.spec import first_reachable
 from .context import HostStaging, StepContext
 from .graphs import GraphCache
 
@@ -179,7 +180,7 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
             if len(table) < need:
                 raise CapacityError("the step was given tokens whose pages were not taken")
             if key[1] is not None:                     # a window group's table may have holes
-                first = max(0, s - key[1] + 1) // P
+                first = first_reachable(key[1], s) // P
                 if any(p < 0 for p in table[first:need]):
                     raise CapacityError("the step was given tokens whose pages were not taken")
     ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=M)

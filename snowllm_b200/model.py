@@ -32,10 +32,14 @@ class Model:
                     raise ConfigError(f"a {layer.block!r} layer has one norm for both sublayers")
             elif (layer.ffn is None) != (layer.ffn_norm is None):
                 raise ConfigError("a layer has a feed-forward and its norm, or neither")
+            extra = dict(layer.block_params)
+            if extra:                              # an arrangement with constants or tensors of its own
+                extra["dtype"] = dtype
             self.blocks.append(block_cls(_make("mixer", layer.mixer, dtype),
                                          _make("ffn", layer.ffn, dtype) if layer.ffn is not None else None,
                                          _make("norm", layer.mixer_norm, dtype),
-                                         _make("norm", layer.ffn_norm, dtype) if layer.ffn_norm is not None else None))
+                                         _make("norm", layer.ffn_norm, dtype) if layer.ffn_norm is not None else None,
+                                         **extra))
         self.final_norm = _make("norm", spec.final_norm, dtype)
         self.head = _make("head", spec.head, dtype)
         self.run = list(spec.run)
@@ -55,9 +59,15 @@ class Model:
 
     # -- structure ------------------------------------------------------------------------
     def parts(self):
+        """Every part that holds tensors, nested ones (a mixer made of two mixers) after the part they sit in."""
+        def walk(part):
+            yield part
+            for inner in getattr(part, "parts", tuple)():
+                yield from walk(inner)
         yield self.embedding
         for b in self.blocks:
-            yield from b.parts()
+            for p in b.parts():
+                yield from walk(p)
         yield self.final_norm
         yield self.head
 
@@ -105,6 +115,8 @@ class Model:
         for i, entry in enumerate(self.run):
             for part in self.blocks[entry.layer].parts():
                 total += of(part, (picked or {}).get(i))
+                for inner in getattr(part, "parts", tuple)():
+                    total += of(inner)
         return total
 
     @property

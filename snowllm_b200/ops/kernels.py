@@ -21,7 +21,7 @@ _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
 P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "elementwise": {
-        "snk_embedding": [P, P, I, P, P, I, I, I, I, P],
+        "snk_embedding": [P, P, I, P, P, I, I, I, I, F, P],
         "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P, P, P, I, P],
         "snk_residual_add": [P, P, LL, P],
         "snk_swiglu": [P, P, I, I, I, I, P],
@@ -84,8 +84,8 @@ _SIGNATURES = {
     "sublayer": {
         "snk_norm_add": [P, P, P, I, P, I, I, F, I, P],
         "snk_cast_rows": [P, P, LL, I, P],
-        "snk_gated_act": [P, P, I, I, I, I, I, P],
-        "snk_head_norm_gate": [P, I, I, F, P, I, P, I, LL, P, I, I, I, F, F, I, P],
+        "snk_gated_act": [P, P, I, I, I, I, F, I, P],
+        "snk_head_norm_gate": [P, I, I, F, P, I, P, I, LL, P, I, I, I, F, F, I, I, P],
         "snk_act_rows": [P, P, LL, I, I, P],
         "snk_rms_cols": [P, LL, I, P, I, P, I, I, F, I, P],
         "snk_add_dyt": [P, P, P, P, P, P, I, P, P, P, I, P, P, I, I, I, P],
@@ -97,13 +97,20 @@ _SIGNATURES = {
         "snk_heads_to_rows": [P, P, I, I, I, I, P],
     },
     "attention_split": {
-        "snk_split_prepare": [P, LL, I, I, I, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
+        "snk_split_prepare": [P, LL, I, I, I, P, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
         "snk_split_attention_tile_rows": [I, I, I, I, I, I, I],
         "snk_split_attention_decode_chunk": [I, I, I, I, I, I],
-        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, I, I, P, I, P],
+        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, P, P, I, I, P, I, P],
     },
     "mlstm": {
         "snk_mlstm": [P, LL, I, I, I, I, I, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, P],
+    },
+    "decay_memory": {
+        "snk_decay_memory": [P, LL, I, I, I, I, P, P, I, P, P, I, F, P, P, P, P, P, P, I, I, I, I, P],
+    },
+    "streams": {
+        "snk_streams_norm": [P, P, P, P, P, P, P, I, P, P, P, P, I, I, F, P, P, I, I, I, I, I, P],
+        "snk_pair_norm_mix": [P, P, P, P, I, F, F, F, P, I, I, P],
     },
     "sampling": {
         "snk_argmax": [P, P, I, I, P],
@@ -230,8 +237,8 @@ def _small(t: torch.Tensor, what: str, compute: torch.dtype) -> int:
 # --- elementwise -----------------------------------------------------------------------
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None,
-              pending: torch.Tensor | None = None) -> torch.Tensor:
-    """Float rows of ``table`` (compute dtype) at int32 ``ids``: the start of the residual stream.
+              pending: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """Float rows of ``table`` (compute dtype) at int32 ``ids``, times ``scale``: the start of the residual stream.
     An id -(i + 1) reads its token from ``pending[i]`` (int32, on the device)."""
     M = ids.numel()
     V, H = table.shape
@@ -243,7 +250,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None =
         out = torch.empty(M, H, dtype=torch.float32, device=table.device)
     _chk(out, "embedding output", torch.float32, (M, H))
     check(fn("snk_embedding")(_ptr(ids), _ptr(pending), pending.numel() if pending is not None else 0,
-                              _ptr(table), _ptr(out), M, H, V, code_of(table.dtype), _stream()), "embedding",
+                              _ptr(table), _ptr(out), M, H, V, code_of(table.dtype), float(scale), _stream()),
+          "embedding",
           work=lambda: (M * H * table.element_size() + _nbytes(out, ids), 0))
     return out
 
@@ -872,8 +880,17 @@ def gather_rows(x, rows, div=1, out=None):
 ROUTE_GEMM_MIN_ROWS = 64
 
 
-def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
-    """(ids int32 [M, k], weights float [M, k]) of the sigmoid router, computed in float."""
+def _route_flags(norm_topk_prob, scoring: str) -> int:
+    """The routing kernels' ``norm_topk`` argument: bit 0 renormalises the picks' weights by their sum, bit 1
+    scores with a softmax over all experts instead of a sigmoid per expert."""
+    if scoring not in ("sigmoid", "softmax"):
+        raise KernelError(f"router scoring {scoring!r} (known: sigmoid, softmax)")
+    return int(bool(norm_topk_prob)) | (2 if scoring == "softmax" else 0)
+
+
+def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling, scoring: str = "sigmoid"):
+    """(ids int32 [M, k], weights float [M, k]) of the router, computed in float: a sigmoid per expert, or
+    (``scoring`` "softmax") a softmax over all experts' logits; the k largest scores are picked."""
     M, H = x.shape
     dtype = x.dtype
     _chk(x, "router input", (torch.float32, torch.bfloat16))
@@ -895,7 +912,7 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
                                       _stream()), "gemm_tc_parts",
               work=lambda: (_nbytes(x, router_w) + M * E * 4 * max(planes.value, 1), 2 * M * E * H))
         check(fn("snk_moe_topk")(_ptr(parts), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
-                                 int(bool(norm_topk_prob)), float(scaling), 0, planes.value, _stream()), "moe_topk")
+                                 _route_flags(norm_topk_prob, scoring), float(scaling), 0, planes.value, _stream()), "moe_topk")
         return ids, wts
     if M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_skinny_ok(router_w, x):
         # many rows: the logits are a tensor-core product with float accumulation and float output.  The few
@@ -903,10 +920,10 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
         # leaves the logits transposed, [E, M].
         logits = gemm_skinny(router_w, x, out_dtype=torch.float32, rows_hint=min(E, 64))
         check(fn("snk_moe_topk")(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
-                                 int(bool(norm_topk_prob)), float(scaling), 1, 1, _stream()), "moe_topk")
+                                 _route_flags(norm_topk_prob, scoring), float(scaling), 1, 1, _stream()), "moe_topk")
         return ids, wts
     check(fn("snk_moe_route")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(ids), _ptr(wts), M, H, E,
-                              top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
+                              top_k, _route_flags(norm_topk_prob, scoring), float(scaling), code_of(dtype), _stream()),
           "moe_route", work=lambda: (_nbytes(x, router_w, ids, wts), 2 * M * E * H))
     return ids, wts
 
@@ -914,14 +931,14 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
 ROUTE_FUSED_MAX_ROWS = 32      # up to here: logits spread over the GPU, selection and sort in one block
 
 
-def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling):
+def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling, scoring: str = "sigmoid"):
     """Routing and the sort by expert together: (ids, weights, offsets, pair_pos, sorted_pair) as
     `moe_route` and `moe_sort` give them.  The few rows of a decode step take two launches made for
     them; a row's logits are the same numbers on every path but the tensor-core one."""
     M, H = x.shape
     E = router_w.shape[0]
     if M > ROUTE_FUSED_MAX_ROWS or 8 * E * min(M, 32) + 8 * M * top_k > 48 * 1024:
-        ids, wts = moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling)
+        ids, wts = moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling, scoring)
         return (ids, wts) + moe_sort(ids, E)
     dtype = x.dtype
     _chk(x, "router input", (torch.float32, torch.bfloat16))
@@ -938,7 +955,7 @@ def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling):
     logits, wts = floats[:M * E], floats[M * E:].view(M, top_k)
     check(fn("snk_moe_route_sort")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(logits), _ptr(ids), _ptr(wts),
                                    _ptr(offsets), _ptr(pair_pos), _ptr(sorted_pair), M, H, E, top_k,
-                                   int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
+                                   _route_flags(norm_topk_prob, scoring), float(scaling), code_of(dtype), _stream()),
           "moe_route_sort", launches=2, work=lambda: (_nbytes(x, router_w, ints, floats), 2 * M * E * H))
     return ids, wts, offsets, pair_pos, sorted_pair
 
@@ -1105,31 +1122,38 @@ def cast_rows(x, dtype, out=None):
     return out
 
 
-def gated_act(gate_up, activation: str, interleaved: bool = False, out=None):
-    """[M, 2I] -> [M, I]: act(gate) * up with ``activation`` one of silu, relu, gelu_tanh.  Columns are
+GATED_ACTIVATIONS = dict(ACTIVATIONS, swish_clamp=4)
+
+
+def gated_act(gate_up, activation: str, interleaved: bool = False, out=None, limit: float = 0.0):
+    """[M, 2I] -> [M, I]: act(gate) * up with ``activation`` one of silu, relu, gelu_tanh, or ``swish_clamp``:
+    g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).  Columns are
     (gate | up), or with ``interleaved`` blocks of 8 gate columns followed by the 8 up columns."""
     M, two_i = gate_up.shape
     _chk(gate_up, "gated activation input", (torch.float32, torch.bfloat16))
-    if activation not in ACTIVATIONS:
-        raise KernelError(f"activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    if activation not in GATED_ACTIVATIONS:
+        raise KernelError(f"activation {activation!r} (known: {', '.join(GATED_ACTIVATIONS)})")
     if two_i % 2:
         raise KernelError("gated activation input needs an even width")
     inter = two_i // 2
     if out is None:
         out = torch.empty(M, inter, dtype=gate_up.dtype, device=gate_up.device)
     _chk(out, "gated activation output", gate_up.dtype, (M, inter))
-    check(fn("snk_gated_act")(_ptr(gate_up), _ptr(out), M, inter, int(interleaved), ACTIVATIONS[activation],
-                              code_of(gate_up.dtype), _stream()), "gated_act",
+    check(fn("snk_gated_act")(_ptr(gate_up), _ptr(out), M, inter, int(interleaved), GATED_ACTIVATIONS[activation],
+                              float(limit), code_of(gate_up.dtype), _stream()), "gated_act",
           work=lambda: (_nbytes(gate_up, out), 0))
     return out
 
 
 def head_norm_gate(a, heads, dv, eps, dtype, *, second=0, lam=0.0, weight=None, gate=None, gate_col=0,
-                   mult=1.0, out=None):
+                   mult=1.0, out=None, gate_act: str = "sigmoid"):
     """Per (row, head): o = a[..., :dv] - lam * a[..., second:second + dv] (the second term only with
     ``second``), o / sqrt(mean(o^2) + eps) * mult, times ``weight`` [heads*dv] and times
-    sigmoid(gate[:, gate_col + head*dv + c]) where given.  ``a``: float [M, heads, width]; ``gate``: a
-    2-D float or compute-dtype tensor whose columns from ``gate_col`` on hold the gate's pre-activation."""
+    sigmoid(gate[:, gate_col + head*dv + c]) where given (``gate_act`` "silu": times silu of it).  ``a``:
+    float [M, heads, width]; ``gate``: a 2-D float or compute-dtype tensor whose columns from ``gate_col`` on
+    hold the gate's pre-activation."""
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError(f"gate activation {gate_act!r} (known: sigmoid, silu)")
     _chk(a, "head values", torch.float32)
     M = a.shape[0]
     stride = a.numel() // max(M * heads, 1)
@@ -1150,7 +1174,8 @@ def head_norm_gate(a, heads, dv, eps, dtype, *, second=0, lam=0.0, weight=None, 
         out = torch.empty(M, heads * dv, dtype=dtype, device=a.device)
     _chk(out, "gated heads", dtype, (M, heads * dv))
     check(fn("snk_head_norm_gate")(_ptr(a), stride, int(second), float(lam), _ptr(weight), w32, g_ptr, g32, g_ld,
-                                   _ptr(out), M, heads, dv, float(eps), float(mult), code_of(dtype), _stream()),
+                                   _ptr(out), M, heads, dv, float(eps), float(mult), int(gate_act == "silu"),
+                                   code_of(dtype), _stream()),
           "head_norm_gate", work=lambda: (_nbytes(a, out) + M * heads * dv * (gate.element_size() if gate is not None else 0), 0))
     return out
 
@@ -1373,21 +1398,26 @@ def heads_to_rows(x, out=None):
 # --- attention over split pools ---------------------------------------------------------------
 
 def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, rot_dim, rot_mult, positions,
-                  row_seg, block_table, page_size, kpool, vpool, nq, nkv, maps, dk, dv, write_kv=True):
+                  row_seg, block_table, page_size, kpool, vpool, nq, nkv, maps, dk, dv, write_kv=True,
+                  proj_bias=None, plain_norm=False):
     """Rows of a fused projection ``proj`` [M, width] (q at column ``q_off`` as [nq, dk], k at ``k_off`` as
     [nkv*maps, dk], v at ``v_off`` as [nkv, dv]): per-head RMS norm of q and k (if weights are given),
     rotation of the first ``rot_dim`` elements of each head by angle position * inv_freq with cos and sin
     times ``rot_mult`` (if ``inv_freq``), k and v written to their pools
-    ([pages, nkv, page_size, maps*dk] and [pages, nkv, page_size, dv]); returns q [M, nq, dk]."""
+    ([pages, nkv, page_size, maps*dk] and [pages, nkv, page_size, dv]); returns q [M, nq, dk].
+    ``proj_bias`` (float [width]): added to the projection's columns first.  ``plain_norm``: q and k over
+    their root mean square without a weight."""
     M, width = proj.shape
     dtype = proj.dtype
     _chk(proj, "projection", (torch.float32, torch.bfloat16))
     need = max(q_off + nq * dk, (k_off + nkv * maps * dk) if write_kv else 0, (v_off + nkv * dv) if write_kv else 0)
     if width < need:
         raise KernelError(f"projection of width {width} holds no {need} columns")
-    has_norm = q_gamma is not None
+    has_norm = q_gamma is not None or plain_norm
     g32 = 0
-    if has_norm:
+    if proj_bias is not None:
+        _chk(proj_bias, "projection bias", torch.float32, (width,))
+    if q_gamma is not None:
         g32 = _small(q_gamma, "q norm weight", dtype)
         if _small(k_gamma, "k norm weight", dtype) != g32:
             raise KernelError("q and k norm weights must share a dtype")
@@ -1407,7 +1437,8 @@ def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, ro
                               f"{page_size}, {maps * dk}] and [pages, {nkv}, {page_size}, {dv}]")
     q_out = torch.empty(M, nq, dk, dtype=dtype, device=proj.device)
     check(fn("snk_split_prepare")(
-        _ptr(proj), width, q_off, k_off, v_off, _ptr(q_gamma), _ptr(k_gamma), g32, int(has_norm), float(eps),
+        _ptr(proj), width, q_off, k_off, v_off, _ptr(proj_bias), _ptr(q_gamma), _ptr(k_gamma), g32, int(has_norm),
+        float(eps),
         _ptr(inv_freq), rot, float(rot_mult), _ptr(positions), _ptr(row_seg), _ptr(block_table),
         block_table.shape[1], page_size, _ptr(kpool), _ptr(vpool), _ptr(q_out), M, nq, nkv * maps, nkv, dk, dv,
         int(write_kv), code_of(dtype), _stream()), "split_prepare",
@@ -1432,12 +1463,22 @@ def split_attention_decode_chunk(nq: int, nkv: int, maps: int, dk: int, dv: int,
     return int(fn("snk_split_attention_decode_chunk")(int(nq), int(nkv), int(maps), int(dk), int(dv), code_of(dtype)))
 
 
+def reach_code(window=None, block=None) -> int:
+    """How the attention kernels are told which keys a query reaches: W > 0 the last W keys, -C < 0 the keys
+    of the query's own block of C positions (counted from position 0), 0 every earlier key."""
+    if window and block:
+        raise KernelError("a sliding window and a block-local mask exclude one another")
+    return int(window) if window else (-int(block) if block else 0)
+
+
 def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, *, maps=1, window=None,
                     bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None, num_chunks=1, scratch=None,
-                    chunk=SPLIT_ATTENTION_CHUNK):
+                    chunk=SPLIT_ATTENTION_CHUNK, block=None, head_scale=None, sink=None):
     """Causal attention of q [M, nq, dk] (nq = heads * maps) over keys [pages, nkv, page_size, maps*dk] and
     values [pages, nkv, page_size, dv]; query head (h, map) reads the key at offset map*dk of its kv head.
-    ``window``: the last ``window`` keys only.  ``bias`` float [nq, L]: added to the scaled score by
+    ``window``: the last ``window`` keys only; ``block``: the keys of the query's own block of ``block``
+    positions only.  ``head_scale`` float [nq]: a factor per query head on ``scale``.  ``sink`` float [nq]: one
+    more term exp(sink) in each row's softmax sum, with no key and no value.  ``bias`` float [nq, L]: added to the scaled score by
     distance min(i - j, L - 1).  ``tiles`` int32 [n, 2] = (first row, rows <= tile_rows) of consecutive
     rows of one request, covering the step; None: every row alone.  ``num_chunks`` > 1 (rows alone only):
     a row's keys are cut into chunks of ``chunk`` (``split_attention_decode_chunk``) at absolute positions, one block each, and
@@ -1460,6 +1501,10 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
         _chk(bias, "distance bias", torch.float32)
         if bias.dim() != 2 or bias.shape[0] != nq:
             raise KernelError(f"distance bias of shape {tuple(bias.shape)}, want [{nq}, distances]")
+    for name, t in (("head scale", head_scale), ("sink", sink)):
+        if t is not None:
+            _chk(t, name, torch.float32, (nq,))
+    reach = reach_code(window, block)
     n_tiles = M
     if tiles is not None:
         _chk(tiles, "attention tiles", torch.int32)
@@ -1485,18 +1530,18 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
 
     def work():
         pos = positions.cpu().long()
-        keys = (pos + 1).clamp(max=int(window)) if window else pos + 1
+        keys = (pos + 1).clamp(max=int(window)) if window else (pos % int(block) + 1 if block else pos + 1)
         total = int(keys.sum())
         return (-(-total // max(tile_rows, 1)) * nkv * (maps * dk + dv) * kpool.element_size() + _nbytes(q, out),
                 2 * nq * (dk + dv) * total)
     check(fn("snk_split_attention")(
         _ptr(q), _ptr(kpool), _ptr(vpool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
         _ptr(row_seg), _ptr(tiles), n_tiles, int(tile_rows), _ptr(out), int(out_dtype == torch.float32 and dtype != torch.float32),
-        nq, nkv, int(maps), dk, dv, int(window or 0), float(scale), _ptr(bias),
-        bias.shape[1] if bias is not None else 0, int(chunk), num_chunks, _ptr(scratch),
+        nq, nkv, int(maps), dk, dv, reach, float(scale), _ptr(bias),
+        bias.shape[1] if bias is not None else 0, _ptr(head_scale), _ptr(sink), int(chunk), num_chunks, _ptr(scratch),
         code_of(dtype), _stream()), "split_attention", work=work)
     if num_chunks > 1:
-        check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, int(window or 0),
+        check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, reach,
                                         int(chunk), num_chunks, code_of(out_dtype), c_void_p(0), _stream()),
               "attention_merge", work=lambda: (M * nq * (dv + 2) * 4 * num_chunks + _nbytes(out), 0))
     return out
@@ -1533,4 +1578,152 @@ def mlstm(proj, q_off, k_off, v_off, i_off, f_off, bias_i, bias_f, cap, cu_seqle
                           _ptr(state_n), _ptr(state_m), _ptr(out), B, heads, dk, dv, _stream()), "mlstm",
           work=lambda: (M * (2 * heads * dk + 2 * heads * dv) * 4 + 2 * B * heads * dk * dv * 4,
                         4 * M * heads * dk * dv))
+    return out
+
+
+# --- decayed matrix memory (linear attention with a state of fixed size) ----------------------------
+
+def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, state, heads, dk, dv, *,
+                 gate_bias=None, gate_low=None, decay=None, inv_freq=None, rot_dim=0, k_scale=1.0, positions=None,
+                 out=None):
+    """S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per (segment, head) over a flat batch.  ``proj``:
+    float [M, width] with q at ``q_off`` and k (or the gate's pre-activation) at ``k_off`` ([heads, dk] each)
+    and v at ``v_off`` ([heads, dv]).  Gated form (``gate_bias`` and ``gate_low`` over [heads*dk]): f = low +
+    (1 - low) * sigmoid(z + bias), a = f, k = 1 - f, q = silu(projection).  Fixed form (``decay`` float
+    [heads]): a = decay[head] for every row; the first ``rot_dim`` elements of q and k of each head turn with
+    ``positions`` (split halves, ``inv_freq`` float [rot_dim/2]); k times ``k_scale`` afterwards.  ``state``
+    (float [slots, heads, dk, dv]) is read unless a segment starts at 0, and brought up to date.  Returns
+    the raw head outputs, float [M, heads*dv]."""
+    M, width = proj.shape
+    _chk(proj, "memory projection", torch.float32)
+    B = seg_start.numel()
+    _chk(cu_seqlens, "cu_seqlens", torch.int32, (B + 1,))
+    _chk(seg_start, "seg_start", torch.int32, (B,))
+    _chk(seg_slot, "seg_slot", torch.int32, (B,))
+    _chk(state, "memory state", torch.float32, (state.shape[0], heads, dk, dv))
+    if width < max(q_off + heads * dk, k_off + heads * dk, v_off + heads * dv):
+        raise KernelError(f"memory projection of width {width} is too narrow")
+    gated = gate_bias is not None
+    g32 = 0
+    if gated:
+        g32 = _small(gate_bias, "gate bias", torch.float32)
+        if gate_low is None or _small(gate_low, "gate lower bound", torch.float32) != g32:
+            raise KernelError("gate bias and lower bound must both be given, in one dtype")
+        _chk(gate_bias, "gate bias", shape=(heads * dk,))
+        _chk(gate_low, "gate lower bound", shape=(heads * dk,))
+    else:
+        if decay is None:
+            raise KernelError("a memory without a gate needs a decay per head")
+        _chk(decay, "decay", torch.float32, (heads,))
+        if inv_freq is not None and rot_dim:
+            _chk(inv_freq, "inv_freq", torch.float32, (rot_dim // 2,))
+            _chk(positions, "positions", torch.int32, (M,))
+        else:
+            inv_freq, rot_dim = None, 0
+    if out is None:
+        out = torch.empty(M, heads * dv, dtype=torch.float32, device=proj.device)
+    _chk(out, "memory output", torch.float32, (M, heads * dv))
+    check(fn("snk_decay_memory")(_ptr(proj), width, q_off, k_off, v_off, 0 if gated else 1, _ptr(gate_bias),
+                                 _ptr(gate_low), g32, _ptr(decay), _ptr(inv_freq), int(rot_dim), float(k_scale),
+                                 _ptr(positions), _ptr(cu_seqlens), _ptr(seg_start), _ptr(seg_slot), _ptr(state),
+                                 _ptr(out), B, heads, dk, dv, _stream()), "decay_memory",
+          work=lambda: (M * (2 * heads * dk + 2 * heads * dv) * 4 + 2 * B * heads * dk * dv * 4,
+                        4 * M * heads * dk * dv))
+    return out
+
+
+# --- several residual streams ------------------------------------------------------------------------
+
+class StreamsDelta:
+    """A residual stream kept as ``S`` streams (``streams`` float [M, S, W]) with the last sublayer's update
+    still pending: its output ``y`` (a float tensor, an ``ExpertSum`` or a ``DeltaSum``), the matrix ``mix``
+    (float [S, S], indexed [from, to]) and the weights ``out`` (float [S]): X'[t] = sum_s mix[s, t] X[s] +
+    out[t] y.  The norm that follows applies it in its own kernel (``streams_norm``)."""
+
+    def __init__(self, streams, y, mix, out):
+        self.streams, self.y, self.mix, self.out = streams, y, mix, out
+        self.shape = (streams.shape[0], streams.shape[2])
+
+    def total(self) -> torch.Tensor:
+        """The sum of the streams after the pending update, float [M, W] (for taps and tests; not a kernel path)."""
+        y = self.y.dense() if hasattr(self.y, "dense") else self.y
+        new = torch.einsum("st,msw->mtw", self.mix, self.streams) + self.out[None, :, None] * y[:, None, :]
+        return new.sum(1)
+
+    def dense(self):
+        raise KernelError("several residual streams do not reduce to one delta: the norm that follows must be one "
+                          "that reads streams (group_rmsnorm)")
+
+
+def streams_norm(streams, weight, groups, eps, dtype, *, init=None, update: StreamsDelta | None = None,
+                 read=None, rows=None, out=None):
+    """The seam between two sublayers of a stream kept as ``streams`` float [M, S, W]: set the streams to S
+    copies of ``init`` [M, W] (if given), apply the pending ``update`` (if given; its ``y`` may be in pieces),
+    form u = sum_s read[s] X[s] (``read`` None: the plain sum) and normalise it in ``groups`` equal parts,
+    times ``weight``.  With ``rows`` only those rows come out and the streams stay untouched."""
+    M, S, W = streams.shape
+    _chk(streams, "streams", torch.float32)
+    if init is not None:
+        _chk(init, "stream start", torch.float32, (M, W))
+    da = db = moe = None
+    mix = outw = None
+    if update is not None:
+        if update.streams is not streams:
+            raise KernelError("the pending update belongs to other streams")
+        y = update.y
+        if isinstance(y, DeltaSum):
+            da, y = y.a, y.b
+        if isinstance(y, ExpertSum):
+            moe = y
+            _chk(moe.y, "expert outputs", torch.float32)
+            _chk(moe.pair_pos, "pair positions", torch.int32, (M * moe.weights.shape[1],))
+            _chk(moe.weights, "top-k weights", torch.float32)
+        elif da is None:
+            da = y
+        else:
+            db = y
+        for t in (da, db):
+            if t is not None:
+                _chk(t, "sublayer output", torch.float32, (M, W))
+        mix, outw = update.mix, update.out
+        _chk(mix, "stream mix", torch.float32, (S, S))
+        _chk(outw, "stream out weights", torch.float32, (S,))
+    if read is not None:
+        _chk(read, "stream read weights", torch.float32, (S,))
+    w32 = _small(weight, "norm weight", dtype)
+    _chk(weight, "norm weight", shape=(W,))
+    R = M if rows is None else rows.numel()
+    if rows is not None:
+        _chk(rows, "norm rows", torch.int32)
+    if out is None:
+        out = torch.empty(R, W, dtype=dtype, device=streams.device)
+    _chk(out, "norm output", dtype, (R, W))
+    k = moe.weights.shape[1] if moe else 0
+    check(fn("snk_streams_norm")(_ptr(streams), _ptr(init), _ptr(da), _ptr(db), _ptr(moe.y if moe else None),
+                                 _ptr(moe.pair_pos if moe else None), _ptr(moe.weights if moe else None), k,
+                                 _ptr(mix), _ptr(outw), _ptr(read), _ptr(weight), w32, int(groups), float(eps),
+                                 _ptr(out), _ptr(rows), R, S, W, int(update is not None), code_of(dtype), _stream()),
+          "streams_norm",
+          work=lambda: (R * W * 4 * ((S if init is None else 1) + (S if rows is None else 0)
+                                     + (da is not None) + (db is not None) + k) + _nbytes(out), 0))
+    return out
+
+
+def pair_norm_mix(a, b, wa, wb, ca, cb, eps, out=None):
+    """ca * a / rms(a) * wa + cb * b / rms(b) * wb over the width, float [M, W]: the outputs of two mixers
+    side by side, each normalised with a weight of its own."""
+    M, W = a.shape
+    _chk(a, "left output", torch.float32)
+    _chk(b, "right output", torch.float32, (M, W))
+    w32 = _small(wa, "left weight", torch.bfloat16)
+    if _small(wb, "right weight", torch.bfloat16) != w32:
+        raise KernelError("the two weights must share a dtype")
+    _chk(wa, "left weight", shape=(W,))
+    _chk(wb, "right weight", shape=(W,))
+    if out is None:
+        out = torch.empty(M, W, dtype=torch.float32, device=a.device)
+    _chk(out, "mixed output", torch.float32, (M, W))
+    check(fn("snk_pair_norm_mix")(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), w32, float(ca), float(cb), float(eps),
+                                  _ptr(out), M, W, _stream()), "pair_norm_mix",
+          work=lambda: (_nbytes(a, b, out), 0))
     return out

@@ -1,7 +1,7 @@
 """Windowed grouped-query attention mixers whose keys and values have widths of their own
 (csrc/attention_split.cu): keys of ``head_dim``, values of ``v_head_dim``, kept in two pools.
 
-Two kinds are built on one class:
+Three kinds are built on one class:
 
 * ``bias_attention``: one softmax map per head; a learned bias is added to the scaled score, chosen by
   head and by a bucket of the distance i - j (``DistanceBuckets``).  No rotation.
@@ -11,7 +11,13 @@ Two kinds are built on one class:
   mean square and scaled by (1 - offset); the heads are gated by sigmoid(W_g x) before the output
   product.  Rotary positions (plain or stretched) on the first ``rot_dim`` elements of every map.
 
-Both: per-head RMS norm of q and k with one weight of ``head_dim`` shared by all heads (and maps), before
+* ``sink_attention``: one map per head, no positions at all; biased projections; q and k over their root
+  mean square per head without a weight; a learned factor per head on the scale (``temp``); a learned sink
+  per head, one more term exp(sink) in the softmax's sum that has no key and no value; and a block-local
+  mask: position i reads j <= i of its own block of ``block`` positions only (blocks counted from position
+  0 of the sequence, whatever the cut into steps).
+
+The first two: per-head RMS norm of q and k with one weight of ``head_dim`` shared by all heads (and maps), before
 the rotation; ``window`` keeps the last ``window`` keys.  Scores, softmax weights and the per-head
 statistics are float whatever the compute dtype.  A layer that reads another layer's cache
 (``reads_cache``) has no key and value tensors at all: it projects q (and the gate) alone and attends
@@ -29,7 +35,7 @@ from ..ops import kernels, linear
 from . import attention_plan as plan
 from .base import Part
 from .registry import lookup, register_mixer
-from .spec import INIT_ONES, KEEP_F32, KEEP_SMALL, PagedKVSpec, TensorSpec
+from .spec import INIT_BIAS, INIT_ONES, KEEP_F32, KEEP_SMALL, PagedKVSpec, TensorSpec
 
 
 class DistanceBuckets:
@@ -91,11 +97,17 @@ def attention_tiles(ctx, tile_rows: int):
 class MapsAttention(Part):
     libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "attention_split", "attention", "sublayer")
     maps = 1
+    norm_weights = True        # the per-head norm of q and k has a weight (False: the plain root mean square)
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  v_head_dim: int, scale: float, qk_norm_eps: float | None, window: int | None = None,
-                 cache_window: int | None = None, position: dict | None = None, reads_cache: bool = False):
+                 cache_window: int | None = None, position: dict | None = None, reads_cache: bool = False,
+                 block: int | None = None):
         super().__init__(dtype, names)
+        if block is not None and (window is not None or cache_window is not None or reads_cache or block < 1):
+            raise ConfigError("a block-local mask stands alone: no window, no shared cache, a positive size")
+        self.block = block
+        self.proj_bias = self.head_scale = self.sink = None      # float tensors a kind may bind
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
         if (num_heads // num_kv_heads) * self.maps > 32:
@@ -134,7 +146,7 @@ class MapsAttention(Part):
 
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.maps * self.head_dim, self.cache_window, self.v_head_dim,
-                           separate=True)
+                           separate=True, block=self.block)
 
     def declare(self, has):
         H, dk, dv, n = self.hidden_size, self.head_dim, self.v_head_dim, self.names
@@ -143,7 +155,7 @@ class MapsAttention(Part):
             specs += [TensorSpec("k_proj", n["k_proj"], (self.num_kv_heads * self.maps * dk, H)),
                       TensorSpec("v_proj", n["v_proj"], (self.num_kv_heads * dv, H))]
         specs.append(TensorSpec("out_proj", n["out_proj"], (H, self.num_heads * dv)))
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.norm_weights:
             specs.append(TensorSpec("q_norm", n["q_norm"], (dk,), INIT_ONES, KEEP_SMALL))
             if not self.reads_cache:
                 specs.append(TensorSpec("k_norm", n["k_norm"], (dk,), INIT_ONES, KEEP_SMALL))
@@ -177,7 +189,8 @@ class MapsAttention(Part):
                                   inv_freq, rot_dim, getattr(self.position, "magnitude", 1.0), ctx.positions,
                                   ctx.row_seg, cache.block_table, cache.page_size, kpool, vpool, self.nq,
                                   self.num_kv_heads, self.maps, self.head_dim, self.v_head_dim,
-                                  write_kv=owns_cache)
+                                  write_kv=owns_cache, proj_bias=self.proj_bias,
+                                  plain_norm=self.qk_norm_eps is not None and not self.norm_weights)
         ctx.tap("attention_q", q)
         decode_only = max(ctx.host_seg_len) <= 1
         tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
@@ -186,7 +199,7 @@ class MapsAttention(Part):
         if decode_only:
             # rows of decoded tokens: their keys in chunks, one block each, merged in chunk order
             chunk = self._decode_chunk
-            num_chunks = plan.chunks(ctx, self.window, None, chunk)
+            num_chunks = plan.chunks(ctx, self.window, None, chunk, block=self.block)
             if self.window:                # a captured step plans for its longest sequence; a window spans fewer
                 num_chunks = min(num_chunks, (self.window - 1) // chunk + 2)
             if num_chunks > 1:
@@ -194,7 +207,8 @@ class MapsAttention(Part):
         out = kernels.split_attention(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
                                       ctx.row_seg, self.scale, maps=self.maps, window=self.window, bias=self.bias,
                                       tiles=attention_tiles(ctx, tile_rows), tile_rows=tile_rows,
-                                      out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch, chunk=chunk)
+                                      out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch, chunk=chunk,
+                                      block=self.block, head_scale=self.head_scale, sink=self.sink)
         ctx.tap("attention_o", out)
         return proj, out
 
@@ -267,5 +281,38 @@ class DiffAttention(MapsAttention):
         return linear(heads, self.wo, out_dtype=torch.float32)
 
 
+class SinkAttention(MapsAttention):
+    """One map per head, no positions; biased projections, weightless q/k norms, a factor and a sink per
+    head, a block-local mask (``block`` None: plain causal)."""
+    norm_weights = False
+
+    def __init__(self, dtype, names, *, biased: bool = True, **kw):
+        super().__init__(dtype, names, **kw)
+        self.biased = biased
+
+    def declare(self, has):
+        n, dk, dv = self.names, self.head_dim, self.v_head_dim
+        specs = super().declare(has) + [TensorSpec("temp", n["temp"], (self.num_heads,), INIT_ONES, KEEP_F32),
+                                        TensorSpec("sink", n["sink"], (self.num_heads,), INIT_BIAS, KEEP_F32)]
+        if self.biased:
+            specs += [TensorSpec("q_bias", n["q_bias"], (self.num_heads * dk,), INIT_BIAS, KEEP_F32),
+                      TensorSpec("k_bias", n["k_bias"], (self.num_kv_heads * dk,), INIT_BIAS, KEEP_F32),
+                      TensorSpec("v_bias", n["v_bias"], (self.num_kv_heads * dv,), INIT_BIAS, KEEP_F32)]
+        return specs
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.head_scale = tensors["temp"].float().contiguous()
+        self.sink = tensors["sink"].float().contiguous()
+        if self.biased:
+            bias = torch.cat([tensors[k].float() for k in ("q_bias", "k_bias", "v_bias")])
+            self.proj_bias = torch.cat((bias, bias.new_zeros(self.w_in.shape[0] - bias.numel()))).contiguous()
+
+    def forward(self, ctx, x, cache, owns_cache=True):
+        _, out = self._attend(ctx, x, cache, owns_cache, self.dtype)
+        return linear(out.view(ctx.M, -1), self.wo, out_dtype=torch.float32)
+
+
+register_mixer("sink_attention", SinkAttention)
 register_mixer("bias_attention", BiasAttention)
 register_mixer("diff_attention", DiffAttention)

@@ -50,15 +50,20 @@ def _positions(ctx, rows):
     return ctx.host_positions if rows is None else ctx.host_positions[np.asarray(rows, dtype=np.int64)]
 
 
-def chunks(ctx, window=None, rows=None, chunk: int = ATTENTION_CHUNK) -> int:
-    """The most chunks of ``chunk`` keys that a row (of ``rows``, or of the step) spans.  A captured
-    step is planned for the longest sequence its launches may ever serve."""
+def chunks(ctx, window=None, rows=None, chunk: int = ATTENTION_CHUNK, block=None) -> int:
+    """The most chunks of ``chunk`` keys that a row (of ``rows``, or of the step) spans; ``window``: a row
+    reaches its last ``window`` keys only; ``block``: the keys of its own block of ``block`` positions only.
+    A captured step is planned for the longest sequence its launches may ever serve."""
     if ctx.capture_max_len is not None:
-        return max(1, -(-ctx.capture_max_len // chunk))
+        n = max(1, -(-ctx.capture_max_len // chunk))
+        return min(n, (block - 1) // chunk + 2) if block else n
     pos = _positions(ctx, rows)
     if len(pos) == 0:
         return 1
-    lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
+    if block:
+        lo = pos - pos % block
+    else:
+        lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
     return int((pos // chunk - lo // chunk).max()) + 1
 
 

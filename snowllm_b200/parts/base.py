@@ -46,7 +46,8 @@ class Part:
         """Take the loaded tensors (keyed by TensorSpec.local), fuse or reshape as needed."""
 
     def parts(self):
-        """Parts nested in this one (their tensors are declared and bound through it)."""
+        """Parts nested in this one (a mixer made of two mixers): the model declares and binds their tensors as
+        it does this part's own."""
         return ()
 
     def bytes_read(self, bound: Mapping[str, int], picked: int | None = None) -> int:

@@ -13,9 +13,10 @@ from .spec import TensorSpec
 class Embedding(Part):
     libraries = ("elementwise",)
 
-    def __init__(self, dtype, names, *, vocab_size: int, hidden_size: int):
+    def __init__(self, dtype, names, *, vocab_size: int, hidden_size: int, scale: float = 1.0):
+        """``scale``: a constant that multiplies every row on its way into the stream."""
         super().__init__(dtype, names)
-        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
         self.weight = None
 
     def declare(self, has):
@@ -29,7 +30,7 @@ class Embedding(Part):
 
     def forward(self, ctx):
         """The float residual stream [M, H] of the step's tokens."""
-        return kernels.embedding(ctx.token_ids, self.weight, pending=ctx.pending_tokens)
+        return kernels.embedding(ctx.token_ids, self.weight, pending=ctx.pending_tokens, scale=self.scale)
 
 
 class LinearHead(Part):

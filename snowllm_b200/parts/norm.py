@@ -1,8 +1,12 @@
 """Norms over the hidden size, fused with the residual sum that precedes them: RMSNorm
 (snowllm/ops/norm.py:11-30; snowllm/models/lfm2/layers.py:99-104) and Dynamic Tanh, which computes no
-statistics at all: tanh(alpha * x) * weight + bias with one learned number alpha."""
+statistics at all: tanh(alpha * x) * weight + bias with one learned number alpha; and the RMS norm in groups,
+which also reads a residual stream that is kept as several streams."""
 from __future__ import annotations
 
+import torch
+
+from ..errors import ConfigError
 from ..ops import kernels
 from .base import Part
 from .registry import register_norm
@@ -65,5 +69,47 @@ class DynamicTanh(Part):
         return kernels.add_dyt(residual, delta, self.weight, self.bias, self.alpha, self.dtype, rows=rows)
 
 
+class GroupRMSNorm(Part):
+    """RMS norm in ``groups`` equal consecutive parts of the width: each part over its own
+    sqrt(mean(part^2) + eps), the whole times ``weight``.  ``groups`` 1 is the plain RMS norm.  It reads a plain
+    float residual (``residual += delta`` first) or, when ``delta`` is a ``kernels.StreamsDelta``, a stream
+    kept as several streams: the pending update is applied and the streams are read with ``read`` weights
+    (None: their plain sum), all in the one kernel."""
+    libraries = ("streams",)
+    fusable_rms = False
+
+    def __init__(self, dtype, names, *, size: int, eps: float, groups: int = 1):
+        super().__init__(dtype, names)
+        if groups < 1 or size % groups:
+            raise ConfigError(f"a norm over {size} in {groups} groups: the width must be a multiple of the groups")
+        self.size, self.eps, self.groups = size, float(eps), int(groups)
+        self.weight = None
+
+    def declare(self, has):
+        return [TensorSpec("weight", self.names["weight"], (self.size,), INIT_ONES, KEEP_SMALL)]
+
+    def bind(self, tensors):
+        self.weight = tensors["weight"]
+
+    def read_streams(self, ctx, streams, *, init=None, update=None, read=None, rows=None):
+        """The norm of sum_s read[s] X[s] after ``init`` and the pending ``update`` have been applied."""
+        return kernels.streams_norm(streams, self.weight, self.groups, self.eps, self.dtype, init=init,
+                                    update=update, read=read, rows=rows)
+
+    def forward(self, ctx, residual, delta=None, rows=None):
+        if isinstance(delta, kernels.StreamsDelta):
+            return self.read_streams(ctx, delta.streams, update=delta, rows=rows)
+        # one stream: the residual itself, with the identity as its update
+        M, W = residual.shape
+        one = ctx.memo.get("streams_identity")
+        if one is None:
+            one = ctx.memo["streams_identity"] = torch.ones(1, 1, dtype=torch.float32, device=residual.device)
+        streams, update = residual.view(M, 1, W), None
+        if delta is not None:
+            update = kernels.StreamsDelta(streams, delta, one, one.view(1))
+        return self.read_streams(ctx, streams, update=update, rows=rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("group_rmsnorm", GroupRMSNorm)
 register_norm("dyt", DynamicTanh)

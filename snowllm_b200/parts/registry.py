@@ -43,5 +43,5 @@ def kinds(family: str) -> list[str]:
 
 
 def _load_builtin() -> None:
-    from . import (attention, attention_latent, attention_maps, block, embedding, ffn_dense, ffn_moe, mlstm, norm,  # noqa: F401
-                   position, short_conv)
+    from . import (attention, attention_latent, attention_maps, block, decay_memory, embedding, ffn_dense,  # noqa: F401
+                   ffn_moe, mixer_pair, mlstm, norm, position, short_conv)

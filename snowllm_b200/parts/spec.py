@@ -56,6 +56,7 @@ class LayerSpec:
     ffn: PartSpec | None            # None (with ffn_norm None): a layer of the mixer's sublayer alone
     mixer_norm: PartSpec
     ffn_norm: PartSpec | None
+    block_params: Mapping[str, Any] = field(default_factory=dict)   # constants and tensor names of the arrangement itself
 
 
 @dataclass(frozen=True)
@@ -82,11 +83,22 @@ class ModelSpec:
 
 # --- what a mixer asks of the cache manager -------------------------------------------
 
+def first_reachable(reach: int | None, pos: int) -> int:
+    """The first position that a query at ``pos`` (or later) can still read under ``reach``
+    (``PagedKVSpec.reach``)."""
+    if reach is None:
+        return 0
+    if reach > 0:
+        return max(0, pos - reach + 1)
+    return pos - pos % (-reach)
+
+
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Rows that grow with the sequence, kept in pages.  ``window`` None keeps every row; an integer keeps
     the last ``window`` positions (the query's own included), so pages that fall wholly behind the window
-    are given back.
+    are given back.  ``block`` (instead of a window): a query reaches the rows of its own block of ``block``
+    positions only (blocks counted from position 0), so pages wholly before the current block are given back.
 
     The spec chooses the layout of its pools (``pool_shapes``); the cache manager only makes them.
     Keys and values of one width lie in one tensor [pages, 2, kv heads, page_size, head_dim].  With
@@ -101,6 +113,14 @@ class PagedKVSpec:
     v_head_dim: int | None = None
     cache_dtype: str | None = None
     separate: bool = False
+    block: int | None = None
+
+    @property
+    def reach(self) -> int | None:
+        """What the cache manager groups layers by: None every row, W > 0 a window of W, -C a block of C."""
+        if self.window and self.block:
+            raise ValueError("a cache keeps a window or a block, not both")
+        return self.window if self.window else (-self.block if self.block else None)
 
     @property
     def fused(self) -> bool:
