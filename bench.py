@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine at the layer sizes of the LFM2.5 models, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--config 8b-a1b|dense-1.2b|dense-2.6b]
-    python bench.py --design beledra|zafopel   (another design beside the closest existing model at equal size; one JSON line)
+    python bench.py --design beledra|zafopel|toderax   (another design beside the closest existing model at equal size; one JSON line)
                     [--batch B] [--context C] [--dtype bfloat16|float32] [--impl ours|reference]
 
 Prints ONE JSON line.  Without flags: LFM2.5-8B-A1B sizes, 8 requests at context 8,192.
@@ -159,12 +159,51 @@ def _lfm2_moe_like(width: int, layers: int, ff: int, vocab: int = 65536) -> dict
             "use_expert_bias": True, "routed_scaling_factor": 1.0}
 
 
+def _toderax(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """Toderax at sizes that resemble a real model's layers: four residual streams and norms in four groups;
+    per three layers one gated matrix memory (HGRN2: heads of 128 rows and 128 columns) and two pairs of
+    block-local attention with sinks (heads of 64, one kv head per four heads, blocks of 1,024 positions)
+    beside a retention memory (heads of 128 rows and 256 columns, the first 64 dimensions turning); every
+    token goes to 4 of 32 experts of ff/8 and to a shared expert of ff/8."""
+    heads = width // 64
+    mlp = {"kind": "moe", "expert": {"ff": ff // 8, "limit": 7.0}, "router": {"experts": 32, "top": 4},
+           "shared": {"ff": ff // 8, "limit": 7.0}}
+    r_heads = max(width // 256, 1)
+    pair = {"left": {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 64, "vdim": 64, "scale": 0.125,
+                     "mask": {"size": 1024}},
+            "right": {"heads": r_heads, "dim": 128, "vdim": 256, "rot": {"dims": 64, "base": 10000.0},
+                      "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(r_heads - 1, 1)) for h in range(r_heads)]}}
+    memory = {"heads": width // 128, "dim": 128, "vdim": 128}
+    out = [{"type": "hgrn2", "mixer": memory, "mlp": mlp} if i % 3 == 0 else
+           {"type": "parallel", "mixer": pair, "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Toderax", "vocab": vocab, "width": width, "streams": 4, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5, "groups": 4}, "layers": json.loads(json.dumps(out))}
+
+
+def _lfm2_moe_hybrid_like(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """The closest existing model at equal size: LFM2 with routed experts at equal width and depth, a short
+    convolution wherever the other design has a memory alone and attention (heads of 64, one kv head per four)
+    wherever it has a pair, 4 of 32 experts of ff/8 in every layer but the first, which is dense."""
+    heads = width // 64
+    return {"architectures": ["Lfm2MoeForCausalLM"], "model_type": "lfm2_moe", "vocab_size": vocab,
+            "hidden_size": width, "num_hidden_layers": layers,
+            "layer_types": ["conv" if i % 3 == 0 else "full_attention" for i in range(layers)],
+            "num_attention_heads": heads, "num_key_value_heads": max(heads // 4, 1), "conv_L_cache": 3,
+            "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_word_embeddings": True,
+            "max_position_embeddings": 128000, "intermediate_size": ff, "num_dense_layers": 1, "num_experts": 32,
+            "num_experts_per_tok": 4, "moe_intermediate_size": ff // 8, "norm_topk_prob": True,
+            "use_expert_bias": True, "routed_scaling_factor": 1.0}
+
+
 DESIGN_SIZES = {"w2048-l12": (2048, 12, 8192), "w1024-l6": (1024, 6, 4096)}
 # design -> (its name, its configuration at a size, the closest existing model at that size, what that is)
 DESIGNS = {"beledra": ("Beledra", _beledra, ("lfm2_dense", _lfm2_like),
                        "dense LFM2 at equal width, depth, feed-forward width and head counts"),
            "zafopel": ("Zafopel", _zafopel, ("lfm2_moe", _lfm2_moe_like),
-                       "LFM2 with routed experts at equal width, depth, head count and size, expert count and width")}
+                       "LFM2 with routed experts at equal width, depth, head count and size, expert count and width"),
+           "toderax": ("Toderax", _toderax, ("lfm2_moe_hybrid", _lfm2_moe_hybrid_like),
+                       "LFM2 with routed experts at equal width and depth: a short convolution where the design has a "
+                       "memory alone, attention with equal head counts where it has a pair, equal expert count and width")}
 
 
 def design_compare(a) -> dict:

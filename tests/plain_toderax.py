@@ -167,9 +167,10 @@ def hyper_step(X, t, p: str, sublayer):
     return [sum(t[p + "mix"][s, j] * X[s] for s in range(S)) + t[p + "out"][j] * y for j in range(S)]
 
 
-def forward(model: dict, tokens, dtype=torch.float64, layers_out=None, picks=None):
+def forward(model: dict, tokens, dtype=torch.float64, layers_out=None, picks=None, picks_out=None):
     """Logits [T, vocab] of one sequence from position 0.  ``layers_out``: a list that receives the sum of
-    the streams after every layer.  ``picks``: {layer -> [T, top]} forces the experts' choice."""
+    the streams after every layer.  ``picks``: {layer -> [T, top]} forces the experts' choice; ``picks_out``:
+    a dict that receives {layer -> the choice made}."""
     cfg = model["config"]
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in model["tensors"].items()}
     eps, groups = cfg["norm"]["eps"], cfg["norm"].get("groups", 1)
@@ -191,7 +192,13 @@ def forward(model: dict, tokens, dtype=torch.float64, layers_out=None, picks=Non
         subs = [("hc1.", lambda u: mixer(norm(p + "norm1")(u)))]
         if layer.get("mlp") is not None:
             forced = None if picks is None else picks.get(i)
-            subs.append(("hc2.", lambda u: routed_experts(norm(p + "norm2")(u), t, layer["mlp"], p + "mlp.", forced)[0]))
+
+            def feed_forward(u):
+                y, chosen = routed_experts(norm(p + "norm2")(u), t, layer["mlp"], p + "mlp.", forced)
+                if picks_out is not None:
+                    picks_out[i] = chosen
+                return y
+            subs.append(("hc2.", feed_forward))
         for hc, sub in subs:
             X = hyper_step(X, t, p + hc, sub) if streams else [X[0] + sub(X[0])]
         if layers_out is not None:
