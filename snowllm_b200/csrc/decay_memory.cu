@@ -23,6 +23,20 @@
 // activations and rotations are evaluated there, off the token loop's chain of dependent instructions).
 // The output is the raw o in float [M, H*dv]; per-head norms, weights and gates follow in
 // head_norm_gate (sublayer.cu).
+//
+// A long prompt portion would leave one block per (head, 32 columns) walking thousands of tokens while most
+// SMs idle.  The host then cuts every segment into pieces of consecutive rows (`pieces`: int32 [n, 4] =
+// segment, first row, rows, flags; bit 0 the segment's first piece, bit 1 its last) and three launches
+// replace the one:
+//
+//   collect  every piece but a segment's last walks its tokens from S = 0 and leaves its own sum L_p and
+//            the product D_p of its decays per row in `work` / `work_decay`;
+//   scan     per segment, piece after piece: S_(p+1) = diag(D_p) S_p + L_p, starting from the slot's state
+//            (zero for a fresh request); S_p takes L_p's place in `work`;
+//   emit     every piece walks its tokens again from S_p and writes o; a segment's last piece leaves the
+//            state in the slot.
+//
+// The recurrence is linear in S, so this is the same sum in another order, every term still a float.
 #include "common.cuh"
 
 #define DM_CHUNK 32            // tokens brought in at a time
@@ -31,18 +45,27 @@
 
 enum { DM_GATED = 0, DM_FIXED = 1 };
 
-template <int DKR>
+enum { DM_WHOLE = 0, DM_COLLECT = 1, DM_EMIT = 2 };
+enum { DM_FIRST = 1, DM_LAST = 2 };
+
+template <int DKR, int PHASE>
 __global__ void __launch_bounds__(DM_TPC * DM_COLS)
 decay_memory_kernel(const float* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, int mode,
                     SmallVec gate_bias, SmallVec gate_low, const float* __restrict__ decay,
                     const float* __restrict__ inv_freq, int rot_dim, float k_scale,
                     const int* __restrict__ positions, const int* __restrict__ cu_seqlens,
                     const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
-                    float* __restrict__ state, float* __restrict__ out, int H, int dk, int dv) {
+                    float* __restrict__ state, float* __restrict__ out, int H, int dk, int dv,
+                    const int4* __restrict__ pieces, float* __restrict__ work, float* __restrict__ work_decay) {
   pdl_begin();
   extern __shared__ __align__(16) float dm_sh[];
   constexpr int RPT = DKR / DM_TPC;                      // rows of S per thread
-  const int b = blockIdx.x, h = blockIdx.y;
+  int4 piece = make_int4(blockIdx.x, 0, 0, DM_FIRST | DM_LAST);
+  if (PHASE != DM_WHOLE) {
+    piece = pieces[blockIdx.x];
+    if (PHASE == DM_COLLECT && (piece.w & DM_LAST)) return;
+  }
+  const int b = piece.x, h = blockIdx.y;
   const int sub = threadIdx.x & (DM_TPC - 1);            // which share of the column's rows
   const int c = blockIdx.z * DM_COLS + threadIdx.x / DM_TPC;
   const bool has_col = c < dv;
@@ -52,9 +75,16 @@ decay_memory_kernel(const float* __restrict__ proj, long long ld, int q_off, int
   float* as = ks + DM_CHUNK * dkp;                       // [DM_CHUNK][dkp]  decay of each row of S
   float* vs = as + DM_CHUNK * dkp;                       // [DM_CHUNK][DM_COLS]
 
-  const int row0 = cu_seqlens[b], row1 = cu_seqlens[b + 1];
-  const bool fresh = seg_start[b] == 0;
-  float* Ss = state + ((size_t)seg_slot[b] * H + h) * dk * dv;
+  const int row0 = PHASE == DM_WHOLE ? cu_seqlens[b] : piece.y;
+  const int row1 = PHASE == DM_WHOLE ? cu_seqlens[b + 1] : piece.y + piece.z;
+  // where S comes from (null: zero) and where it goes (null: nowhere)
+  float* slot = state + ((size_t)seg_slot[b] * H + h) * dk * dv;
+  float* mine = PHASE == DM_WHOLE ? nullptr : work + ((size_t)blockIdx.x * H + h) * dk * dv;
+  // (a segment's first piece of several reads what the scan left, not the slot that its last piece writes)
+  const float* from = PHASE == DM_COLLECT ? nullptr
+                    : (piece.w & (DM_FIRST | DM_LAST)) == (DM_FIRST | DM_LAST) ? (seg_start[b] == 0 ? nullptr : slot)
+                    : mine;
+  float* to = PHASE == DM_COLLECT ? mine : (piece.w & DM_LAST) ? slot : nullptr;
 
   // register i*4 + e holds row 4 DM_TPC i + 4 sub + e
   float S[RPT];
@@ -63,8 +93,12 @@ decay_memory_kernel(const float* __restrict__ proj, long long ld, int q_off, int
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int r = 4 * DM_TPC * i + 4 * sub + e;
-      S[i * 4 + e] = (!fresh && has_col && r < dk) ? Ss[(size_t)r * dv + c] : 0.f;
+      S[i * 4 + e] = (from && has_col && r < dk) ? from[(size_t)r * dv + c] : 0.f;
     }
+  float D[PHASE == DM_COLLECT ? RPT : 1];                // the product of each row's decays over the piece
+  if (PHASE == DM_COLLECT)
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) D[i] = 1.f;
   const int col0 = blockIdx.z * DM_COLS;
   const int half = rot_dim >> 1;
   const float head_decay = mode == DM_FIXED ? decay[h] : 0.f;
@@ -127,38 +161,90 @@ decay_memory_kernel(const float* __restrict__ proj, long long ld, int q_off, int
       for (int i = 0; i < RPT / 4; ++i) {
         if (4 * DM_TPC * i < dk) {
           const float4 k4 = *reinterpret_cast<const float4*>(kt + 4 * DM_TPC * i + 4 * sub);
-          const float4 q4 = *reinterpret_cast<const float4*>(qt + 4 * DM_TPC * i + 4 * sub);
           const float4 a4 = *reinterpret_cast<const float4*>(at + 4 * DM_TPC * i + 4 * sub);
-          S[i * 4 + 0] = fmaf(a4.x, S[i * 4 + 0], k4.x * v); acc = fmaf(S[i * 4 + 0], q4.x, acc);
-          S[i * 4 + 1] = fmaf(a4.y, S[i * 4 + 1], k4.y * v); acc = fmaf(S[i * 4 + 1], q4.y, acc);
-          S[i * 4 + 2] = fmaf(a4.z, S[i * 4 + 2], k4.z * v); acc = fmaf(S[i * 4 + 2], q4.z, acc);
-          S[i * 4 + 3] = fmaf(a4.w, S[i * 4 + 3], k4.w * v); acc = fmaf(S[i * 4 + 3], q4.w, acc);
+          S[i * 4 + 0] = fmaf(a4.x, S[i * 4 + 0], k4.x * v);
+          S[i * 4 + 1] = fmaf(a4.y, S[i * 4 + 1], k4.y * v);
+          S[i * 4 + 2] = fmaf(a4.z, S[i * 4 + 2], k4.z * v);
+          S[i * 4 + 3] = fmaf(a4.w, S[i * 4 + 3], k4.w * v);
+          if (PHASE == DM_COLLECT) {
+            D[i * 4 + 0] *= a4.x; D[i * 4 + 1] *= a4.y; D[i * 4 + 2] *= a4.z; D[i * 4 + 3] *= a4.w;
+          } else {
+            const float4 q4 = *reinterpret_cast<const float4*>(qt + 4 * DM_TPC * i + 4 * sub);
+            acc = fmaf(S[i * 4 + 0], q4.x, acc);
+            acc = fmaf(S[i * 4 + 1], q4.y, acc);
+            acc = fmaf(S[i * 4 + 2], q4.z, acc);
+            acc = fmaf(S[i * 4 + 3], q4.w, acc);
+          }
         }
       }
+      if (PHASE != DM_COLLECT) {
 #pragma unroll
-      for (int w = 1; w < DM_TPC; w <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
-      if (has_col && sub == 0) out[(size_t)(t0 + t) * H * dv + (size_t)h * dv + c] = acc;
+        for (int w = 1; w < DM_TPC; w <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+        if (has_col && sub == 0) out[(size_t)(t0 + t) * H * dv + (size_t)h * dv + c] = acc;
+      }
     }
   }
+  if (to)
 #pragma unroll
-  for (int i = 0; i < RPT / 4; ++i)
+    for (int i = 0; i < RPT / 4; ++i)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int r = 4 * DM_TPC * i + 4 * sub + e;
-      if (has_col && r < dk) Ss[(size_t)r * dv + c] = S[i * 4 + e];
+      for (int e = 0; e < 4; ++e) {
+        const int r = 4 * DM_TPC * i + 4 * sub + e;
+        if (has_col && r < dk) to[(size_t)r * dv + c] = S[i * 4 + e];
+      }
+  if (PHASE == DM_COLLECT && blockIdx.z == 0 && threadIdx.x < DM_TPC)
+#pragma unroll
+    for (int i = 0; i < RPT / 4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = 4 * DM_TPC * i + 4 * sub + e;
+        if (r < dk) work_decay[((size_t)blockIdx.x * H + h) * dk + r] = D[i * 4 + e];
+      }
+}
+
+// S_(p+1) = diag(D_p) S_p + L_p over the pieces of one segment; S_p takes L_p's place.  One thread per
+// element of S; segments of one piece have nothing to pass on.
+__global__ void __launch_bounds__(256)
+decay_memory_scan_kernel(const int* __restrict__ cu_pieces, const int4* __restrict__ pieces,
+                         const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                         const float* __restrict__ state, float* __restrict__ work,
+                         const float* __restrict__ work_decay, int H, int dk, int dv) {
+  pdl_begin();
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int p0 = cu_pieces[b], p1 = cu_pieces[b + 1];
+  if (p1 - p0 < 2) return;
+  const int n = dk * dv;
+  for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < n; i += gridDim.z * blockDim.x) {
+    const int r = i / dv;
+    float S = seg_start[b] == 0 ? 0.f : state[((size_t)seg_slot[b] * H + h) * n + i];
+    for (int p = p0; p < p1; ++p) {
+      float* w = work + ((size_t)p * H + h) * n + i;
+      if (p + 1 < p1) {
+        const float L = *w;
+        *w = S;
+        S = fmaf(work_decay[((size_t)p * H + h) * dk + r], S, L);
+      } else {
+        *w = S;
+      }
     }
+  }
 }
 
 // proj: float [M, ld].  mode 0 (gated): gate_bias and gate_low over [H*dk] (float or bfloat16, one flag for
 // both).  mode 1 (fixed): decay float [H]; inv_freq float [rot_dim/2] (null or rot_dim 0: no rotation),
 // positions int32 [M].  state: float [slots, H, dk, dv].  out: float [M, H*dv].
+// n_pieces 0: one block walks a whole segment.  Otherwise pieces int32 [n_pieces, 4], cu_pieces int32 [B+1]
+// (first piece of each segment), work float [n_pieces, H, dk, dv], work_decay float [n_pieces, H, dk].
 SNK_API int snk_decay_memory(const float* proj, long long ld, int q_off, int k_off, int v_off, int mode,
                              const void* gate_bias, const void* gate_low, int gate_f32, const float* decay,
                              const float* inv_freq, int rot_dim, float k_scale, const int* positions,
                              const int* cu_seqlens, const int* seg_start, const int* seg_slot, float* state,
-                             float* out, int B, int H, int dk, int dv, cudaStream_t stream) {
+                             float* out, int B, int H, int dk, int dv, const int* pieces, const int* cu_pieces,
+                             int n_pieces, float* work, float* work_decay, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (H <= 0 || H > 65535 || dk <= 0 || dk > 256 || dv <= 0 || dv > 32 * 65535) return SNK_ERR_SIZE;
+  if (n_pieces < 0 || (n_pieces && (!pieces || !cu_pieces || !work || !work_decay))) return SNK_ERR_SIZE;
+  if (n_pieces && ((uintptr_t)pieces & 15)) return SNK_ERR_ALIGN;
   if (mode == DM_GATED) {
     if (!gate_bias || !gate_low) return SNK_ERR_SIZE;
   } else if (mode == DM_FIXED) {
@@ -171,19 +257,36 @@ SNK_API int snk_decay_memory(const float* proj, long long ld, int q_off, int k_o
   const int slices = (dv + DM_COLS - 1) / DM_COLS;
   const int dkp = (dk + 4 * DM_TPC - 1) / (4 * DM_TPC) * (4 * DM_TPC);
   const size_t smem = (size_t)(DM_CHUNK * (3 * dkp + DM_COLS)) * sizeof(float);
-  dim3 grid(B, H, slices);
-#define DM_LAUNCH(DKR_)                                                                                       \
+#define DM_LAUNCH(DKR_, PHASE_, N_)                                                                           \
   do {                                                                                                        \
+    auto kernel = decay_memory_kernel<DKR_, PHASE_>;                                                          \
     if (smem > 48 * 1024)                                                                                     \
-      cudaFuncSetAttribute(decay_memory_kernel<DKR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    snk_launch(decay_memory_kernel<DKR_>, dim3(grid), dim3(DM_TPC * DM_COLS), smem, stream, proj, ld, q_off,   \
-               k_off, v_off, mode, SmallVec{gate_bias, gate_f32}, SmallVec{gate_low, gate_f32}, decay,        \
-               inv_freq, rot_dim, k_scale, positions, cu_seqlens, seg_start, seg_slot, state, out, H, dk, dv); \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
+    snk_launch(kernel, dim3(N_, H, slices), dim3(DM_TPC * DM_COLS), smem, stream, proj, ld, q_off, k_off,     \
+               v_off, mode, SmallVec{gate_bias, gate_f32}, SmallVec{gate_low, gate_f32}, decay, inv_freq,     \
+               rot_dim, k_scale, positions, cu_seqlens, seg_start, seg_slot, state, out, H, dk, dv,           \
+               reinterpret_cast<const int4*>(pieces), work, work_decay);                                      \
   } while (0)
-  if (dk <= 32) DM_LAUNCH(32);
-  else if (dk <= 64) DM_LAUNCH(64);
-  else if (dk <= 128) DM_LAUNCH(128);
-  else DM_LAUNCH(256);
+#define DM_PHASE(PHASE_, N_)                                                                                  \
+  do {                                                                                                        \
+    if (dk <= 32) DM_LAUNCH(32, PHASE_, N_);                                                                  \
+    else if (dk <= 64) DM_LAUNCH(64, PHASE_, N_);                                                             \
+    else if (dk <= 128) DM_LAUNCH(128, PHASE_, N_);                                                           \
+    else DM_LAUNCH(256, PHASE_, N_);                                                                          \
+  } while (0)
+  if (!n_pieces) {
+    DM_PHASE(DM_WHOLE, B);
+  } else {
+    DM_PHASE(DM_COLLECT, n_pieces);
+    SNK_LAUNCH_CHECK();
+    const int per = (dk * dv + 255) / 256;
+    snk_launch(decay_memory_scan_kernel, dim3(B, H, per < 64 ? per : 64), dim3(256), 0, stream, cu_pieces,
+               reinterpret_cast<const int4*>(pieces), seg_start, seg_slot, (const float*)state, work,
+               (const float*)work_decay, H, dk, dv);
+    SNK_LAUNCH_CHECK();
+    DM_PHASE(DM_EMIT, n_pieces);
+  }
+#undef DM_PHASE
 #undef DM_LAUNCH
   SNK_LAUNCH_CHECK();
   return 0;

@@ -106,7 +106,7 @@ _SIGNATURES = {
         "snk_mlstm": [P, LL, I, I, I, I, I, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, P],
     },
     "decay_memory": {
-        "snk_decay_memory": [P, LL, I, I, I, I, P, P, I, P, P, I, F, P, P, P, P, P, P, I, I, I, I, P],
+        "snk_decay_memory": [P, LL, I, I, I, I, P, P, I, P, P, I, F, P, P, P, P, P, P, I, I, I, I, P, P, I, P, P, P],
     },
     "streams": {
         "snk_streams_norm": [P, P, P, P, P, P, P, I, P, P, P, P, I, I, F, P, P, I, I, I, I, I, P],
@@ -1585,7 +1585,7 @@ def mlstm(proj, q_off, k_off, v_off, i_off, f_off, bias_i, bias_f, cap, cu_seqle
 
 def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, state, heads, dk, dv, *,
                  gate_bias=None, gate_low=None, decay=None, inv_freq=None, rot_dim=0, k_scale=1.0, positions=None,
-                 out=None):
+                 out=None, pieces=None):
     """S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per (segment, head) over a flat batch.  ``proj``:
     float [M, width] with q at ``q_off`` and k (or the gate's pre-activation) at ``k_off`` ([heads, dk] each)
     and v at ``v_off`` ([heads, dv]).  Gated form (``gate_bias`` and ``gate_low`` over [heads*dk]): f = low +
@@ -1593,7 +1593,9 @@ def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, sta
     [heads]): a = decay[head] for every row; the first ``rot_dim`` elements of q and k of each head turn with
     ``positions`` (split halves, ``inv_freq`` float [rot_dim/2]); k times ``k_scale`` afterwards.  ``state``
     (float [slots, heads, dk, dv]) is read unless a segment starts at 0, and brought up to date.  Returns
-    the raw head outputs, float [M, heads*dv]."""
+    the raw head outputs, float [M, heads*dv].  ``pieces`` = (int32 [n, 4] = segment, first row, rows, flags
+    with 1 for a segment's first piece and 2 for its last; int32 [B+1] = first piece of each segment): every
+    piece is walked by blocks of its own, from the state that a scan over the pieces' own sums gives it."""
     M, width = proj.shape
     _chk(proj, "memory projection", torch.float32)
     B = seg_start.numel()
@@ -1623,10 +1625,20 @@ def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, sta
     if out is None:
         out = torch.empty(M, heads * dv, dtype=torch.float32, device=proj.device)
     _chk(out, "memory output", torch.float32, (M, heads * dv))
+    table = cu_pieces = work = work_decay = None
+    n_pieces = 0
+    if pieces is not None:
+        table, cu_pieces = pieces
+        n_pieces = table.shape[0]
+        _chk(table, "memory pieces", torch.int32, (n_pieces, 4))
+        _chk(cu_pieces, "first piece of each segment", torch.int32, (B + 1,))
+        work = torch.empty(n_pieces, heads, dk, dv, dtype=torch.float32, device=proj.device)
+        work_decay = torch.empty(n_pieces, heads, dk, dtype=torch.float32, device=proj.device)
     check(fn("snk_decay_memory")(_ptr(proj), width, q_off, k_off, v_off, 0 if gated else 1, _ptr(gate_bias),
                                  _ptr(gate_low), g32, _ptr(decay), _ptr(inv_freq), int(rot_dim), float(k_scale),
                                  _ptr(positions), _ptr(cu_seqlens), _ptr(seg_start), _ptr(seg_slot), _ptr(state),
-                                 _ptr(out), B, heads, dk, dv, _stream()), "decay_memory",
+                                 _ptr(out), B, heads, dk, dv, _ptr(table), _ptr(cu_pieces), n_pieces, _ptr(work),
+                                 _ptr(work_decay), _stream()), "decay_memory", launches=3 if n_pieces else 1,
           work=lambda: (M * (2 * heads * dk + 2 * heads * dv) * 4 + 2 * B * heads * dk * dv * 4,
                         4 * M * heads * dk * dv))
     return out

@@ -26,6 +26,31 @@ from .registry import lookup, register_mixer
 from .spec import INIT_BIAS, INIT_ONES, KEEP_F32, KEEP_SMALL, SlotStateSpec, TensorSpec
 
 MAX_HEAD_DIM = 256
+PIECE_ROWS = 64        # rows of a prompt portion that one block walks when the step holds a long portion
+
+
+def memory_pieces(ctx, piece_rows: int | None = None):
+    """The step's segments cut into pieces of up to ``piece_rows`` rows for the memory kernel: (int32 [n, 4] =
+    segment, first row, rows, flags with 1 for a segment's first piece and 2 for its last; int32 [B+1] = first
+    piece of each segment), on the device, uploaded once per step.  None when no segment is longer than two
+    pieces: one block per (segment, head, columns) then walks its whole segment, and a captured step holds
+    nothing that changes."""
+    piece_rows = piece_rows or PIECE_ROWS
+    if ctx.capture_max_len is not None or max(ctx.host_seg_len) <= 2 * piece_rows:
+        return None
+    key = ("memory_pieces", piece_rows)
+    if key not in ctx.memo:
+        table, first_piece, first = [], [0], 0
+        for b, n in enumerate(ctx.host_seg_len):
+            cuts = list(range(0, n, piece_rows)) or [0]
+            for r in cuts:
+                table.append((b, first + r, min(piece_rows, n - r), (r == 0) | ((r == cuts[-1]) << 1)))
+            first_piece.append(len(table))
+            first += n
+        flat = [v for row in table for v in row] + first_piece
+        dev = torch.tensor(flat, dtype=torch.int32).pin_memory().to(ctx.device, non_blocking=True)
+        ctx.memo[key] = (dev[:4 * len(table)].view(-1, 4), dev[4 * len(table):])
+    return ctx.memo[key]
 
 
 class _DecayMemory(Part):
@@ -63,7 +88,8 @@ class Hgrn2(_DecayMemory):
         H, dk, dv = self.num_heads, self.head_dim, self.v_head_dim
         proj = linear(x, self.w_in, out_dtype=torch.float32)
         raw = kernels.decay_memory(proj, 0, H * dk, 2 * H * dk, ctx.cu_seqlens, ctx.seg_start, ctx.seg_slot,
-                                   cache.tensors[0], H, dk, dv, gate_bias=self.f_bias, gate_low=self.lower)
+                                   cache.tensors[0], H, dk, dv, gate_bias=self.f_bias, gate_low=self.lower,
+                                   pieces=memory_pieces(ctx))
         ctx.tap("memory_raw", raw)
         heads = kernels.head_norm_gate(raw, H, dv, self.head_norm_eps, self.dtype, weight=self.norm)
         return linear(heads, self.wo, out_dtype=torch.float32)
@@ -99,7 +125,7 @@ class Retention(_DecayMemory):
         inv_freq, rot_dim = self.position.rotary(x.device)
         raw = kernels.decay_memory(proj, 0, H * dk, 2 * H * dk, ctx.cu_seqlens, ctx.seg_start, ctx.seg_slot,
                                    cache.tensors[0], H, dk, dv, decay=self.decay, inv_freq=inv_freq, rot_dim=rot_dim,
-                                   k_scale=dk ** -0.5, positions=ctx.positions)
+                                   k_scale=dk ** -0.5, positions=ctx.positions, pieces=memory_pieces(ctx))
         ctx.tap("memory_raw", raw)
         heads = kernels.head_norm_gate(raw, H, dv, self.head_norm_eps, self.dtype, gate=proj,
                                        gate_col=2 * H * dk + H * dv, gate_act="silu")
