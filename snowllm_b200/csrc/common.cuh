@@ -48,12 +48,22 @@ struct SmallVec {
 };
 
 // The activation on the gate of a gated product's store: act(g) * u.  Codes as the `swiglu` argument of the
-// product entry points carries them: 1 silu, 2 relu, 3 gelu (tanh form).  (0: no gated store.)
-enum { SNK_GLU_SILU = 1, SNK_GLU_RELU = 2, SNK_GLU_GELU_TANH = 3 };
+// product entry points carries them: 1 silu, 2 relu, 3 gelu (tanh form).  (0: no gated store.)  Any other
+// value is the clamped swish, g' * sigmoid(1.702 g') * (u' + 1) with g' = min(g, L) and u' = clamp(u, -L, L):
+// the bits of the positive float L with the lowest three of its mantissa giving way to the code 4 (L is
+// then exact to 2^-20 of itself; `glu_code_clamped` on the host side of each entry point is the inverse).
+enum { SNK_GLU_SILU = 1, SNK_GLU_RELU = 2, SNK_GLU_GELU_TANH = 3, SNK_GLU_SWISH_CLAMP = 4 };
 __device__ __forceinline__ float glu_act(float g, int act) {
   if (act == SNK_GLU_RELU) return fmaxf(g, 0.f);
   if (act == SNK_GLU_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.f + expf(-g));
+}
+__device__ __forceinline__ float glu_out(float g, float u, int act) {
+  if (act <= SNK_GLU_GELU_TANH) return glu_act(g, act) * u;
+  const float limit = __int_as_float(act & ~7);
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
 }
 
 // Four consecutive outputs in the compute dtype, by one store (16-byte aligned for float, 8 for bfloat16).

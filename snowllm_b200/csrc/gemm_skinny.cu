@@ -174,7 +174,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
             const int m = m0 + tok, n = n0 + r;
             if (m < row_end && n + 8 < N) {
               const float gate = red[1][tok][r], up = red[1][tok][r + 8];
-              C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(glu_act(gate, act) * up);
+              C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(glu_out(gate, up, act));
             }
           }
         } else {
@@ -199,7 +199,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
             gate += red[w][tok][r];
             up += red[w][tok][r + 8];
           }
-          C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(glu_act(gate, act) * up);
+          C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(glu_out(gate, up, act));
         }
       }
     } else {

@@ -313,8 +313,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ parts, OutT* __re
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const __nv_bfloat162 v = __floats2bfloat162_rn(glu_act(g[2 * j], act) * u[2 * j],
-                                                     glu_act(g[2 * j + 1], act) * u[2 * j + 1]);
+      const __nv_bfloat162 v = __floats2bfloat162_rn(glu_out(g[2 * j], u[2 * j], act),
+                                                     glu_out(g[2 * j + 1], u[2 * j + 1], act));
       o[j] = *reinterpret_cast<const uint32_t*>(&v);
     }
     *reinterpret_cast<uint4*>(C + b * 8) = make_uint4(o[0], o[1], o[2], o[3]);   // row m, features 8*(b % (N/16))..

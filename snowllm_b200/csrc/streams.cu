@@ -19,7 +19,39 @@
 
 #define SN_MAX_STREAMS 8
 
-template <typename T>
+// VEC consecutive floats of one row (VEC 4: one 16-byte access)
+template <int VEC>
+__device__ __forceinline__ void sn_load(const float* __restrict__ p, float (&v)[VEC]) {
+  if constexpr (VEC == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    v[0] = *p;
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void sn_store(float* __restrict__ p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else *p = v[0];
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void sn_store_out(T* __restrict__ p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) {
+    __align__(16) T t[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) t[e] = from_f<T>(v[e]);
+    if constexpr (sizeof(T) == 2) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(t);
+    else *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(t);
+  } else {
+    *p = from_f<T>(v[0]);
+  }
+}
+
+#define SN_MAX_PIECES 16       // experts' pieces per row whose places and weights are kept in shared memory
+
+// SMAX: the streams the registers hold (S <= SMAX).  VEC: floats per access (4 needs W and W / groups to be
+// multiples of 4 and 16-byte aligned operands).
+template <typename T, int SMAX, int VEC>
 __global__ void streams_norm_kernel(float* __restrict__ X, const float* __restrict__ init,
                                     const float* __restrict__ da, const float* __restrict__ db,
                                     const float* __restrict__ y, const int* __restrict__ pair_pos,
@@ -29,58 +61,103 @@ __global__ void streams_norm_kernel(float* __restrict__ X, const float* __restri
                                     int S, int W, int has_update) {
   pdl_begin();
   extern __shared__ __align__(16) float sn_sh[];         // [W] u, then [groups] 1 / rms
+  __shared__ int piece_at[SN_MAX_PIECES];
+  __shared__ float piece_w[SN_MAX_PIECES];
   float* us = sn_sh;
   float* inv = sn_sh + ((W + 3) & ~3);
   const size_t m = rows ? rows[blockIdx.x] : blockIdx.x;
   float* xr = X + m * S * W;
-  float cm[SN_MAX_STREAMS][SN_MAX_STREAMS], co[SN_MAX_STREAMS], ci[SN_MAX_STREAMS];
+  float cm[SMAX][SMAX], co[SMAX], ci[SMAX];
 #pragma unroll
-  for (int s = 0; s < SN_MAX_STREAMS; ++s) {
+  for (int s = 0; s < SMAX; ++s) {
     co[s] = (has_update && s < S) ? outw[s] : 0.f;
     ci[s] = s < S ? (inw ? inw[s] : 1.f) : 0.f;
 #pragma unroll
-    for (int t = 0; t < SN_MAX_STREAMS; ++t) cm[s][t] = (has_update && s < S && t < S) ? mix[s * S + t] : 0.f;
+    for (int t = 0; t < SMAX; ++t) cm[s][t] = (has_update && s < S && t < S) ? mix[s * S + t] : 0.f;
   }
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float x[SN_MAX_STREAMS];
+  const bool pieces_shared = has_update && k > 0 && k <= SN_MAX_PIECES;
+  if (pieces_shared) {
+    if (threadIdx.x < k) {
+      piece_at[threadIdx.x] = pair_pos[m * k + threadIdx.x];
+      piece_w[threadIdx.x] = pw[m * k + threadIdx.x];
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
+    float x[SMAX][VEC];
     if (init) {
-      const float v = init[m * W + i];
+      float v[VEC];
+      sn_load<VEC>(init + m * W + i, v);
 #pragma unroll
-      for (int s = 0; s < SN_MAX_STREAMS; ++s) x[s] = v;
+      for (int s = 0; s < SMAX; ++s)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[s][e] = v[e];
     } else {
 #pragma unroll
-      for (int s = 0; s < SN_MAX_STREAMS; ++s) x[s] = s < S ? xr[(size_t)s * W + i] : 0.f;
+      for (int s = 0; s < SMAX; ++s) {
+        if (s < S) {
+          sn_load<VEC>(xr + (size_t)s * W + i, x[s]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) x[s][e] = 0.f;
+        }
+      }
     }
-    float u = 0.f;
+    float u[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) u[e] = 0.f;
     if (has_update) {
-      float d = da ? da[m * W + i] : 0.f;
-      if (db) d += db[m * W + i];
+      float d[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) d[e] = 0.f;
+      if (da) sn_load<VEC>(da + m * W + i, d);
+      if (db) {
+        float t[VEC];
+        sn_load<VEC>(db + m * W + i, t);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) d[e] += t[e];
+      }
       if (k) {
-        float e = 0.f;
-        for (int j = 0; j < k; ++j) e = fmaf(pw[m * k + j], y[(size_t)pair_pos[m * k + j] * W + i], e);
-        d += e;
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+        for (int j = 0; j < k; ++j) {
+          const int at = pieces_shared ? piece_at[j] : pair_pos[m * k + j];
+          const float wt = pieces_shared ? piece_w[j] : pw[m * k + j];
+          float t[VEC];
+          sn_load<VEC>(y + (size_t)at * W + i, t);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wt, t[e], acc[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) d[e] += acc[e];
       }
 #pragma unroll
-      for (int t = 0; t < SN_MAX_STREAMS; ++t) {
+      for (int t = 0; t < SMAX; ++t) {
         if (t < S) {
-          float v = 0.f;
+          float v[VEC];
 #pragma unroll
-          for (int s = 0; s < SN_MAX_STREAMS; ++s) v = fmaf(cm[s][t], x[s], v);
-          v = fmaf(co[t], d, v);
-          if (!rows) xr[(size_t)t * W + i] = v;
-          u = fmaf(ci[t], v, u);
+          for (int e = 0; e < VEC; ++e) {
+            v[e] = 0.f;
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s) v[e] = fmaf(cm[s][t], x[s][e], v[e]);
+            v[e] = fmaf(co[t], d[e], v[e]);
+            u[e] = fmaf(ci[t], v[e], u[e]);
+          }
+          if (!rows) sn_store<VEC>(xr + (size_t)t * W + i, v);
         }
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < SN_MAX_STREAMS; ++t) {
+      for (int t = 0; t < SMAX; ++t) {
         if (t < S) {
-          if (init && !rows) xr[(size_t)t * W + i] = x[t];
-          u = fmaf(ci[t], x[t], u);
+          if (init && !rows) sn_store<VEC>(xr + (size_t)t * W + i, x[t]);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) u[e] = fmaf(ci[t], x[t][e], u[e]);
         }
       }
     }
-    us[i] = u;
+    sn_store<VEC>(us + i, u);
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -95,8 +172,13 @@ __global__ void streams_norm_kernel(float* __restrict__ X, const float* __restri
     if (lane == 0) inv[g] = 1.f / sqrtf(ss / (float)part + eps);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < W; i += blockDim.x)
-    out[(size_t)blockIdx.x * W + i] = from_f<T>(us[i] * inv[i / part] * w[i]);
+  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
+    const float scale = inv[i / part];                   // VEC 4: part is a multiple of 4, one group
+    float v[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v[e] = us[i + e] * scale * w[i + e];
+    sn_store_out<T, VEC>(out + (size_t)blockIdx.x * W + i, v);
+  }
 }
 
 // X: float [M, S, W].  init (may be null): float [M, W].  Pending update (has_update): da, db float [M, W]
@@ -113,13 +195,31 @@ SNK_API int snk_streams_norm(float* X, const float* init, const float* da, const
   if (has_update && (!mix || !outw)) return SNK_ERR_SIZE;
   const size_t smem = (size_t)(((W + 3) & ~3) + groups) * sizeof(float);
   if (smem > 200 * 1024) return SNK_ERR_SIZE;
-  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+  const uintptr_t all = (uintptr_t)X | (uintptr_t)init | (uintptr_t)da | (uintptr_t)db | (uintptr_t)y | (uintptr_t)out;
+  const bool vec = W % 4 == 0 && (W / groups) % 4 == 0 && (all & 15) == 0;
+  const int cols = vec ? W / 4 : W;
+  const int threads = cols >= 512 ? 512 : (cols >= 256 ? 256 : 128);
+#define SN_LAUNCH(SMAX_, VEC_)                                                                                \
+  do {                                                                                                        \
+    auto kernel = streams_norm_kernel<T, SMAX_, VEC_>;                                                        \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    snk_launch(kernel, dim3(R), dim3(threads), smem, stream, X, init, da, db, y, pair_pos, pw, k, mix, outw,  \
+               inw, SmallVec{w, w_f32}, groups, eps, static_cast<T*>(out), rows, S, W, has_update);           \
+  } while (0)
   SNK_DISPATCH(dtype, {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(streams_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    snk_launch(streams_norm_kernel<T>, dim3(R), dim3(threads), smem, stream, X, init, da, db, y, pair_pos, pw, k,
-               mix, outw, inw, SmallVec{w, w_f32}, groups, eps, static_cast<T*>(out), rows, S, W, has_update);
+    if (vec) {
+      if (S == 1) SN_LAUNCH(1, 4);
+      else if (S <= 2) SN_LAUNCH(2, 4);
+      else if (S <= 4) SN_LAUNCH(4, 4);
+      else SN_LAUNCH(8, 4);
+    } else {
+      if (S == 1) SN_LAUNCH(1, 1);
+      else if (S <= 2) SN_LAUNCH(2, 1);
+      else if (S <= 4) SN_LAUNCH(4, 1);
+      else SN_LAUNCH(8, 1);
+    }
   });
+#undef SN_LAUNCH
   SNK_LAUNCH_CHECK();
   return 0;
 }

@@ -79,7 +79,7 @@ __device__ __forceinline__ void tc_store_piece(const uint32_t (&r)[32], float* s
         for (int j = 0; j < 4; ++j) {
           const float g0 = __uint_as_float(r[blk * 16 + 2 * j]), g1 = __uint_as_float(r[blk * 16 + 2 * j + 1]);
           const float u0 = __uint_as_float(r[blk * 16 + 8 + 2 * j]), u1 = __uint_as_float(r[blk * 16 + 9 + 2 * j]);
-          const __nv_bfloat162 v = __floats2bfloat162_rn(glu_act(g0, act) * u0, glu_act(g1, act) * u1);
+          const __nv_bfloat162 v = __floats2bfloat162_rn(glu_out(g0, u0, act), glu_out(g1, u1, act));
           p[j] = *reinterpret_cast<const uint32_t*>(&v);
         }
         *reinterpret_cast<uint4*>(dst + blk * 8) = make_uint4(p[0], p[1], p[2], p[3]);

@@ -106,7 +106,7 @@ _SIGNATURES = {
         "snk_mlstm": [P, LL, I, I, I, I, I, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, P],
     },
     "decay_memory": {
-        "snk_decay_memory": [P, LL, I, I, I, I, P, P, I, P, P, I, F, P, P, P, P, P, P, I, I, I, I, P, P, I, P, P, P],
+        "snk_decay_memory": [P, LL, I, I, I, I, P, P, I, P, P, I, F, P, P, P, P, P, P, I, I, I, I, P, P, I, P, P, P, I, P],
     },
     "streams": {
         "snk_streams_norm": [P, P, P, P, P, P, P, I, P, P, P, P, I, I, F, P, P, I, I, I, I, I, P],
@@ -1625,7 +1625,7 @@ def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, sta
     if out is None:
         out = torch.empty(M, heads * dv, dtype=torch.float32, device=proj.device)
     _chk(out, "memory output", torch.float32, (M, heads * dv))
-    table = cu_pieces = work = work_decay = None
+    table = cu_pieces = work = work_decay = prep = None
     n_pieces = 0
     if pieces is not None:
         table, cu_pieces = pieces
@@ -1634,11 +1634,13 @@ def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, sta
         _chk(cu_pieces, "first piece of each segment", torch.int32, (B + 1,))
         work = torch.empty(n_pieces, heads, dk, dv, dtype=torch.float32, device=proj.device)
         work_decay = torch.empty(n_pieces, heads, dk, dtype=torch.float32, device=proj.device)
+        prep = torch.empty(3 if gated else 2, M, heads * dk, dtype=torch.float32, device=proj.device)
     check(fn("snk_decay_memory")(_ptr(proj), width, q_off, k_off, v_off, 0 if gated else 1, _ptr(gate_bias),
                                  _ptr(gate_low), g32, _ptr(decay), _ptr(inv_freq), int(rot_dim), float(k_scale),
                                  _ptr(positions), _ptr(cu_seqlens), _ptr(seg_start), _ptr(seg_slot), _ptr(state),
                                  _ptr(out), B, heads, dk, dv, _ptr(table), _ptr(cu_pieces), n_pieces, _ptr(work),
-                                 _ptr(work_decay), _stream()), "decay_memory", launches=3 if n_pieces else 1,
+                                 _ptr(work_decay), _ptr(prep), M, _stream()), "decay_memory",
+          launches=4 if n_pieces else 1,
           work=lambda: (M * (2 * heads * dk + 2 * heads * dv) * 4 + 2 * B * heads * dk * dv * 4,
                         4 * M * heads * dk * dv))
     return out

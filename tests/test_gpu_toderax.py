@@ -542,7 +542,9 @@ def agree(got, want, dtype, bound=None) -> bool:
     d = d - d.mean(-1, keepdim=True)
     w = want.double() - want.double().mean(-1, keepdim=True)
     rows = torch.sqrt((d * d).mean(-1)) / torch.sqrt((w * w).mean())
-    return int((rows >= bound).sum()) <= max(got.shape[0] // 10, 1) and (len(rows) < 8 or float(rows.median()) < bound / 2)
+    if len(rows) < 8:                                      # too few rows for a share: none far off
+        return float(rows.max()) < 5 * bound
+    return int((rows >= bound).sum()) <= len(rows) // 10 and float(rows.median()) < bound / 2
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
