@@ -1,4 +1,4 @@
 """Kernel entry points (csrc/*.cu through ctypes) and the shape-to-kernel choice for products."""
 from . import kernels  # noqa: F401
-from .linear import (grouped_linear, grouped_linear_swiglu, interleave_gate_up, linear,  # noqa: F401
-                     linear_glu, linear_swiglu)
+from .linear import (grouped_linear, grouped_linear_glu, grouped_linear_swiglu, interleave_gate_up,  # noqa: F401
+                     linear, linear_glu, linear_swiglu)

@@ -12,9 +12,11 @@ bfloat16 operands that neither takes (K no multiple of 8, unaligned views): the 
 from __future__ import annotations
 
 import os
+import struct
 
 import torch
 
+from ..errors import KernelError
 from . import kernels
 
 # Products of very many rows run on pairs of SMs (csrc/gemm_tc2.cu: 256 x 256 tiles, a third less operand traffic).
@@ -81,18 +83,39 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 GLU_CODES = {"silu": 1, "relu": 2, "gelu_tanh": 3}
 
 
-def linear_glu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool, activation: str = "silu") -> torch.Tensor:
+def glu_code(activation: str, limit: float = 0.0) -> int:
+    """The integer that tells a product's gated store what to apply.  The clamped swish travels as the bits
+    of its positive float limit, the lowest three of the mantissa giving way to the code 4 (the limit the store
+    applies is then within 2^-20 of the given one, and equal to it for limits with a short binary
+    expansion)."""
+    if activation == "swish_clamp":
+        if not limit > 0:
+            raise KernelError("the clamped activation needs a positive limit")
+        bits = struct.unpack("<i", struct.pack("<f", float(limit)))[0]
+        return (bits & ~7) | 4
+    return GLU_CODES[activation]
+
+
+def _gated(h: torch.Tensor, interleaved: bool, activation: str, limit: float) -> torch.Tensor:
+    """The gate applied by a kernel of its own, where the product's store could not."""
+    if activation == "silu":
+        return kernels.swiglu(h, interleaved=interleaved)
+    return kernels.gated_act(h, activation, interleaved, limit=limit)
+
+
+def linear_glu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool, activation: str = "silu",
+               limit: float = 0.0) -> torch.Tensor:
     """act(x Wg^T) * (x Wu^T) -> [M, I] with Wg, Wu held in one matrix w13 [2I, K] (plain halves, or
-    interleaved by 8) and ``activation`` one of silu, relu, gelu_tanh.  With the interleaved layout the
-    bfloat16 products apply the gate at their store; otherwise one elementwise kernel follows the product."""
+    interleaved by 8) and ``activation`` one of silu, relu, gelu_tanh, or swish_clamp with its ``limit``
+    (g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)).  With the
+    interleaved layout the bfloat16 products apply the gate at their store; otherwise one elementwise kernel
+    follows the product."""
     if interleaved and kernels.gemm_skinny_ok(x, w13):
-        code = GLU_CODES[activation]
+        code = glu_code(activation, limit)
         if x.shape[0] <= SKINNY_MAX_ROWS:
             return kernels.gemm_skinny(x, w13, swiglu=code)
         return _tc(x, w13, swiglu=code)
-    if activation == "silu":
-        return kernels.swiglu(linear(x, w13), interleaved=interleaved)
-    return kernels.gated_act(linear(x, w13), activation, interleaved)
+    return _gated(linear(x, w13), interleaved, activation, limit)
 
 
 def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torch.Tensor:
@@ -100,14 +123,21 @@ def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torc
     return linear_glu(x, w13, interleaved, "silu")
 
 
-def grouped_linear_swiglu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved: bool):
-    """The grouped form of ``linear_swiglu`` over rows sorted by group (w13 [G, 2I, K])."""
+def grouped_linear_glu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved: bool,
+                       activation: str = "silu", limit: float = 0.0):
+    """The grouped form of ``linear_glu`` over rows sorted by group (w13 [G, 2I, K])."""
     if interleaved and kernels.gemm_skinny_ok(x, w13):
+        code = glu_code(activation, limit)
         if _few_rows_per_group(rows_out, w13.shape[0]):
             hint = min(max_rows_per_group, max(8, 2 * -(-rows_out // w13.shape[0])))
             return kernels.gemm_skinny(x, w13, a_rows=a_rows, a_div=a_div, offsets=offsets, rows_out=rows_out,
-                                       rows_hint=hint, swiglu=True)
+                                       rows_hint=hint, swiglu=code)
         xs = kernels.gather_rows(x, a_rows, a_div) if a_rows is not None else x
-        return _tc(xs, w13, offsets=offsets, swiglu=True)
+        return _tc(xs, w13, offsets=offsets, swiglu=code)
     h = grouped_linear(x, w13, offsets, rows_out, max_rows_per_group, a_rows=a_rows, a_div=a_div)
-    return kernels.swiglu(h, interleaved=interleaved)
+    return _gated(h, interleaved, activation, limit)
+
+
+def grouped_linear_swiglu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved: bool):
+    """``grouped_linear_glu`` with silu."""
+    return grouped_linear_glu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved)

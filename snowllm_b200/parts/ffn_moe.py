@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..errors import ConfigError
-from ..ops import grouped_linear, grouped_linear_swiglu, interleave_gate_up, kernels, linear
+from ..ops import grouped_linear, grouped_linear_glu, interleave_gate_up, kernels, linear, linear_glu
 from .base import Part
 from .registry import register_ffn
 from .spec import INIT_BIAS, KEEP_F32, KEEP_SMALL, TensorSpec
@@ -89,10 +89,12 @@ class SigmoidMoE(Part):
             up = torch.stack([tensors[f"up.{e}"] for e in range(E)])
             self.w2 = torch.stack([tensors[f"down.{e}"] for e in range(E)]).contiguous()
         # gate and up rows interleaved by 8 where the width allows: the product then applies SwiGLU itself
-        self.interleaved = self.intermediate_size % 8 == 0 and self.activation == "silu"
+        self.interleaved = self.intermediate_size % 8 == 0
         self.w13 = interleave_gate_up(gate, up) if self.interleaved else torch.cat((gate, up), 1).contiguous()
         if self.shared is not None:
-            self.shared_w13 = torch.cat((tensors["shared_gate"], tensors["shared_up"]), 0).contiguous()
+            self.shared_interleaved = self.shared["intermediate_size"] % 8 == 0
+            self.shared_w13 = (interleave_gate_up(tensors["shared_gate"], tensors["shared_up"]) if self.shared_interleaved
+                               else torch.cat((tensors["shared_gate"], tensors["shared_up"]), 0).contiguous())
             self.shared_w2 = tensors["shared_down"]
 
     def bytes_read(self, bound, picked=None):
@@ -132,15 +134,13 @@ class SigmoidMoE(Part):
             x, self.router, self.bias, self.top_k, self.norm_topk_prob, self.routed_scaling_factor, self.scoring))
         if self.shared is None:
             return routed
-        act = kernels.gated_act(linear(x, self.shared_w13), self.activation, False, limit=self.shared["limit"])
+        act = linear_glu(x, self.shared_w13, self.shared_interleaved, self.activation, self.shared["limit"])
         return kernels.DeltaSum(linear(act, self.shared_w2, out_dtype=torch.float32), routed)
 
     def _gate_up(self, x, offsets, rows_out, cap, a_rows, a_div):
         """The experts' activated gate|up product over the rows in expert order."""
-        if self.activation == "silu":
-            return grouped_linear_swiglu(x, self.w13, offsets, rows_out, cap, a_rows, a_div, self.interleaved)
-        h = grouped_linear(x, self.w13, offsets, rows_out, cap, a_rows=a_rows, a_div=a_div)
-        return kernels.gated_act(h, self.activation, False, limit=self.limit)
+        return grouped_linear_glu(x, self.w13, offsets, rows_out, cap, a_rows, a_div, self.interleaved,
+                                  self.activation, self.limit or 0.0)
 
     def _experts(self, ctx, x, ids, weights, offsets, pair_pos, sorted_pair):
         M, k = x.shape[0], self.top_k
