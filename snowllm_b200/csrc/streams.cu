@@ -52,7 +52,9 @@ __device__ __forceinline__ void sn_store_out(T* __restrict__ p, const float (&v)
 // SMAX: the streams the registers hold (S <= SMAX).  VEC: floats per access (4 needs W and W / groups to be
 // multiples of 4 and 16-byte aligned operands).
 template <typename T, int SMAX, int VEC>
-__global__ void streams_norm_kernel(float* __restrict__ X, const float* __restrict__ init,
+// (The bound of 768 threads is there for its register limit, 85: three blocks of 256 then share an SM.)
+__global__ void __launch_bounds__(SMAX <= 4 ? 768 : 256)
+streams_norm_kernel(float* __restrict__ X, const float* __restrict__ init,
                                     const float* __restrict__ da, const float* __restrict__ db,
                                     const float* __restrict__ y, const int* __restrict__ pair_pos,
                                     const float* __restrict__ pw, int k, const float* __restrict__ mix,
@@ -67,22 +69,23 @@ __global__ void streams_norm_kernel(float* __restrict__ X, const float* __restri
   float* inv = sn_sh + ((W + 3) & ~3);
   const size_t m = rows ? rows[blockIdx.x] : blockIdx.x;
   float* xr = X + m * S * W;
-  float cm[SMAX][SMAX], co[SMAX], ci[SMAX];
-#pragma unroll
-  for (int s = 0; s < SMAX; ++s) {
-    co[s] = (has_update && s < S) ? outw[s] : 0.f;
-    ci[s] = s < S ? (inw ? inw[s] : 1.f) : 0.f;
-#pragma unroll
-    for (int t = 0; t < SMAX; ++t) cm[s][t] = (has_update && s < S && t < S) ? mix[s * S + t] : 0.f;
+  // the stream weights lie in shared memory (every thread reads the same word): in registers they cost a
+  // third of the threads an SM could hold, and this kernel lives on loads in flight
+  __shared__ float cm[SMAX][SMAX], co[SMAX], ci[SMAX];
+  if (threadIdx.x < SMAX * SMAX) {
+    const int s = threadIdx.x / SMAX, t = threadIdx.x % SMAX;
+    cm[s][t] = (has_update && s < S && t < S) ? mix[s * S + t] : 0.f;
+    if (t == 0) {
+      co[s] = (has_update && s < S) ? outw[s] : 0.f;
+      ci[s] = s < S ? (inw ? inw[s] : 1.f) : 0.f;
+    }
   }
   const bool pieces_shared = has_update && k > 0 && k <= SN_MAX_PIECES;
-  if (pieces_shared) {
-    if (threadIdx.x < k) {
-      piece_at[threadIdx.x] = pair_pos[m * k + threadIdx.x];
-      piece_w[threadIdx.x] = pw[m * k + threadIdx.x];
-    }
-    __syncthreads();
+  if (pieces_shared && threadIdx.x >= 64 && threadIdx.x < 64 + k) {
+    piece_at[threadIdx.x - 64] = pair_pos[m * k + threadIdx.x - 64];
+    piece_w[threadIdx.x - 64] = pw[m * k + threadIdx.x - 64];
   }
+  __syncthreads();
   for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
     float x[SMAX][VEC];
     if (init) {
@@ -164,9 +167,16 @@ __global__ void streams_norm_kernel(float* __restrict__ X, const float* __restri
   const int part = W / groups;
   for (int g = warp; g < groups; g += nwarps) {
     float ss = 0.f;
-    for (int i = lane; i < part; i += 32) {
-      const float v = us[g * part + i];
-      ss = fmaf(v, v, ss);
+    if constexpr (VEC == 4) {
+      for (int i = lane * 4; i < part; i += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(us + g * part + i);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+      }
+    } else {
+      for (int i = lane; i < part; i += 32) {
+        const float v = us[g * part + i];
+        ss = fmaf(v, v, ss);
+      }
     }
     ss = warp_sum(ss);
     if (lane == 0) inv[g] = 1.f / sqrtf(ss / (float)part + eps);
@@ -198,7 +208,11 @@ SNK_API int snk_streams_norm(float* X, const float* init, const float* da, const
   const uintptr_t all = (uintptr_t)X | (uintptr_t)init | (uintptr_t)da | (uintptr_t)db | (uintptr_t)y | (uintptr_t)out;
   const bool vec = W % 4 == 0 && (W / groups) % 4 == 0 && (all & 15) == 0;
   const int cols = vec ? W / 4 : W;
-  const int threads = cols >= 512 ? 512 : (cols >= 256 ? 256 : 128);
+  // Many rows: blocks of 256 threads, of which an SM holds three (four streams in registers) in different
+  // phases, kept its loads in flight better than one block of 512 (a 2,048-row seam 63 -> 43 us).  Few rows:
+  // every block has an SM to itself and the widest one is through soonest.  At least 64 + SN_MAX_PIECES
+  // threads, and SMAX^2.
+  const int threads = cols >= 512 && R < 592 && S <= 4 ? 512 : (cols >= 256 ? 256 : 128);
 #define SN_LAUNCH(SMAX_, VEC_)                                                                                \
   do {                                                                                                        \
     auto kernel = streams_norm_kernel<T, SMAX_, VEC_>;                                                        \

@@ -180,13 +180,19 @@ def _nbytes(*tensors) -> int:
 
 
 def check(status: int, what: str, launches: int = 1, work=None) -> None:
-    """``work``: a function giving (bytes, flops) of the call; evaluated only when the ledger is on."""
+    """``work``: a function giving (bytes, flops) of the call, or a list of them, one per launch in launch
+    order; evaluated only when the ledger is on."""
     global _launches
     if status == 0:
         _launches += launches
         if ledger is not None and launches:
-            nbytes, flops = work() if work is not None else (None, None)
-            ledger.append((what, launches, nbytes, flops))
+            done = work() if work is not None else (None, None)
+            if isinstance(done, list):
+                if len(done) != launches:
+                    raise KernelError(f"{what}: work of {len(done)} launches for {launches}")
+                ledger.extend((what, 1, nbytes, flops) for nbytes, flops in done)
+            else:
+                ledger.append((what, launches, done[0], done[1]))
         return
     if status in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[status]}")
@@ -1640,10 +1646,21 @@ def decay_memory(proj, q_off, k_off, v_off, cu_seqlens, seg_start, seg_slot, sta
                                  _ptr(positions), _ptr(cu_seqlens), _ptr(seg_start), _ptr(seg_slot), _ptr(state),
                                  _ptr(out), B, heads, dk, dv, _ptr(table), _ptr(cu_pieces), n_pieces, _ptr(work),
                                  _ptr(work_decay), _ptr(prep), M, _stream()), "decay_memory",
-          launches=4 if n_pieces else 1,
-          work=lambda: (M * (2 * heads * dk + 2 * heads * dv) * 4 + 2 * B * heads * dk * dv * 4,
-                        4 * M * heads * dk * dv))
+          launches=4 if n_pieces else 1, work=lambda: _decay_memory_work(M, B, heads, dk, dv, n_pieces, gated))
     return out
+
+
+def _decay_memory_work(M, B, H, dk, dv, pieces, gated):
+    """(bytes, flops) of the memory kernel; with pieces one pair per launch: prepare, collect, scan, emit.  A
+    token's step on one element of S is three operations (a S, k v, their sum) and two more where o is formed."""
+    rows_k, rows_v, cells = M * H * dk * 4, M * H * dv * 4, H * dk * dv
+    if not pieces:
+        return (2 * rows_k + 2 * rows_v + 2 * B * cells * 4, 5 * M * cells)
+    prep = (3 if gated else 2) * rows_k
+    return [(2 * rows_k + prep, 0),
+            (prep - rows_k + rows_v + pieces * cells * 4, 3 * M * cells),
+            (2 * pieces * cells * 4 + B * cells * 4, 2 * pieces * cells),
+            (prep + 2 * rows_v + pieces * cells * 4 + B * cells * 4, 5 * M * cells)]
 
 
 # --- several residual streams ------------------------------------------------------------------------
