@@ -500,6 +500,39 @@ def test_pair_mix_clamped_gate_silu_head_gate_softmax_router_and_scaled_embeddin
     assert torch.equal(got.cpu(), table[ids.long()].float() * 2.5)
 
 
+def clamped_swish(g, u, limit):
+    g = g.clamp(max=limit)
+    return g * torch.sigmoid(plain.SWISH_SLOPE * g) * (u.clamp(-limit, limit) + 1.0)
+
+
+@pytest.mark.parametrize("rows", [3, 130, 4300])
+@pytest.mark.parametrize("limit", [0.75, 2.3])
+def test_products_clamp_and_gate_at_their_store(rows, limit):
+    """The few-rows product, the tcgen05 product and the product on pairs of SMs with the clamped swish, plain
+    and grouped, against float64 products of the same bfloat16 operands; a limit that many values exceed, and
+    one whose bits do not end in zeros."""
+    from snowllm_b200.ops import grouped_linear_glu, interleave_gate_up, linear_glu
+    g = torch.Generator().manual_seed(rows)
+    K, inter, groups = 64, 40, 3
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(groups, inter, K, generator=g) * 0.3).to(torch.bfloat16)
+    up = (torch.randn(groups, inter, K, generator=g) * 0.3).to(torch.bfloat16)
+    got = linear_glu(x.cuda(), interleave_gate_up(gate[0], up[0]).cuda(), True, "swish_clamp", limit)
+    want = clamped_swish(x.double() @ gate[0].double().T, x.double() @ up[0].double().T, limit)
+    assert got.shape == (rows, inter)
+    assert bool(((got.cpu().double() - want).abs() <= 0.008 * want.abs() + 2e-3).all())     # one bfloat16 rounding
+    assert cases.relative_error(got.cpu(), want) < 0.004
+    # rows in group order, unequal groups, one of them empty when there are few rows
+    cuts = [0, rows // 2, rows // 2, rows] if rows < 10 else [0, rows // 5, rows // 2, rows]
+    offsets = torch.tensor(cuts, dtype=torch.int32).cuda()
+    got = grouped_linear_glu(x.cuda(), interleave_gate_up(gate, up).cuda(), offsets, rows, rows, None, 1, True,
+                             "swish_clamp", limit)
+    want = torch.cat([clamped_swish(x[a:b].double() @ gate[e].double().T, x[a:b].double() @ up[e].double().T, limit)
+                      for e, (a, b) in enumerate(zip(cuts[:-1], cuts[1:]))])
+    assert bool(((got.cpu().double() - want).abs() <= 0.008 * want.abs() + 2e-3).all())
+    assert cases.relative_error(got.cpu(), want) < 0.004
+
+
 # --- one model with everything: cuts, batches, reuse ------------------------------------------------
 
 @pytest.fixture(scope="module")
