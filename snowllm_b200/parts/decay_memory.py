@@ -16,6 +16,8 @@ One fused product leaves the projections in float; gates, decays, angles, state,
 statistics are float whatever the compute dtype."""
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from ..errors import ConfigError
@@ -27,6 +29,27 @@ from .spec import INIT_BIAS, INIT_ONES, KEEP_F32, KEEP_SMALL, SlotStateSpec, Ten
 
 MAX_HEAD_DIM = 256
 PIECE_ROWS = 64        # rows of a prompt portion that one block walks when the step holds a long portion
+
+
+PIECE_CHOICES = (48, 56, 64, 72, 80, 96)
+BLOCKS_PER_SM = 2      # of the memory kernel with heads of 128 rows, by its registers
+
+
+def piece_rows_for(seg_lens, blocks_per_piece: int, sms: int) -> int:
+    """The piece size among PIECE_CHOICES whose blocks fill the SMs in the fewest and shortest rounds: a launch
+    takes about (rounds of blocks) x (rows a block walks), and 512 blocks on 296 places wait for a second round
+    that is a quarter empty where 592 smaller ones fill two.  Ties go to PIECE_ROWS, then to the larger piece."""
+    places = max(sms * BLOCKS_PER_SM, 1)
+
+    def cost(rows):
+        blocks = sum(-(-n // rows) for n in seg_lens) * blocks_per_piece
+        return -(-blocks // places) * rows
+    return min(PIECE_CHOICES, key=lambda rows: (cost(rows), rows != PIECE_ROWS, -rows))
+
+
+@functools.lru_cache(maxsize=None)
+def _sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
 
 
 def memory_pieces(ctx, piece_rows: int | None = None):
@@ -68,6 +91,15 @@ class _DecayMemory(Part):
     def cache_spec(self):
         return SlotStateSpec(((self.num_heads, self.head_dim, self.v_head_dim),), ("f32",))
 
+    def _pieces(self, ctx):
+        """The step's pieces at the size that suits this layer's heads (a block serves 128 columns of a wide
+        head, 32 of a narrow one)."""
+        if ctx.capture_max_len is not None or PIECE_ROWS not in PIECE_CHOICES:
+            return memory_pieces(ctx)
+        cols = 128 if self.v_head_dim > 64 else 32
+        per_piece = self.num_heads * -(-self.v_head_dim // cols)
+        return memory_pieces(ctx, piece_rows_for(ctx.host_seg_len, per_piece, _sm_count(ctx.device)))
+
 
 class Hgrn2(_DecayMemory):
     def declare(self, has):
@@ -89,7 +121,7 @@ class Hgrn2(_DecayMemory):
         proj = linear(x, self.w_in, out_dtype=torch.float32)
         raw = kernels.decay_memory(proj, 0, H * dk, 2 * H * dk, ctx.cu_seqlens, ctx.seg_start, ctx.seg_slot,
                                    cache.tensors[0], H, dk, dv, gate_bias=self.f_bias, gate_low=self.lower,
-                                   pieces=memory_pieces(ctx))
+                                   pieces=self._pieces(ctx))
         ctx.tap("memory_raw", raw)
         heads = kernels.head_norm_gate(raw, H, dv, self.head_norm_eps, self.dtype, weight=self.norm)
         return linear(heads, self.wo, out_dtype=torch.float32)
@@ -125,7 +157,7 @@ class Retention(_DecayMemory):
         inv_freq, rot_dim = self.position.rotary(x.device)
         raw = kernels.decay_memory(proj, 0, H * dk, 2 * H * dk, ctx.cu_seqlens, ctx.seg_start, ctx.seg_slot,
                                    cache.tensors[0], H, dk, dv, decay=self.decay, inv_freq=inv_freq, rot_dim=rot_dim,
-                                   k_scale=dk ** -0.5, positions=ctx.positions, pieces=memory_pieces(ctx))
+                                   k_scale=dk ** -0.5, positions=ctx.positions, pieces=self._pieces(ctx))
         ctx.tap("memory_raw", raw)
         heads = kernels.head_norm_gate(raw, H, dv, self.head_norm_eps, self.dtype, gate=proj,
                                        gate_col=2 * H * dk + H * dv, gate_act="silu")

@@ -284,3 +284,16 @@ def test_bench_design_option_builds_both_models_at_equal_size():
         assert (routed.num_experts, routed.top_k, routed.intermediate_size) == \
                (theirs_routed.num_experts, theirs_routed.top_k, theirs_routed.intermediate_size)
         assert routed.shared is not None and ours.blocks[0].streams == 4
+
+
+def test_piece_size_fills_the_rounds_of_blocks():
+    from snowllm_b200.parts.decay_memory import PIECE_CHOICES, PIECE_ROWS, piece_rows_for
+    # 16 blocks a piece on 296 places: 37 pieces of 56 rows fill two rounds, 32 of 64 leave the second a quarter empty
+    assert piece_rows_for([2048], 16, 148) == 56
+    # equal cost: the standing size
+    assert piece_rows_for([8192], 16, 148) == PIECE_ROWS
+    # room for every block at any size: the smallest pieces are through soonest
+    assert piece_rows_for([200, 130], 4, 148) == min(PIECE_CHOICES)
+    # whatever the segments, a size of the list
+    for lens in ([1], [97, 3, 4000], [129] * 7):
+        assert piece_rows_for(lens, 3, 20) in PIECE_CHOICES
