@@ -17,6 +17,7 @@ statistics are float whatever the compute dtype."""
 from __future__ import annotations
 
 import functools
+import os
 
 import torch
 
@@ -32,6 +33,7 @@ PIECE_ROWS = 64        # rows of a prompt portion that one block walks when the 
 
 
 PIECE_CHOICES = (48, 56, 64, 72, 80, 96)
+FIXED_PIECE_ROWS = int(os.environ.get("SNOWLLM_B200_PIECE_ROWS", "0"))    # one size for every layer (A/B runs)
 BLOCKS_PER_SM = 2      # of the memory kernel with heads of 128 rows, by its registers
 
 
@@ -96,6 +98,8 @@ class _DecayMemory(Part):
         head, 32 of a narrow one)."""
         if ctx.capture_max_len is not None or PIECE_ROWS not in PIECE_CHOICES:
             return memory_pieces(ctx)
+        if FIXED_PIECE_ROWS:
+            return memory_pieces(ctx, FIXED_PIECE_ROWS)
         cols = 128 if self.v_head_dim > 64 else 32
         per_piece = self.num_heads * -(-self.v_head_dim // cols)
         return memory_pieces(ctx, piece_rows_for(ctx.host_seg_len, per_piece, _sm_count(ctx.device)))
