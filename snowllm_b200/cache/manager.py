@@ -1,7 +1,8 @@
 """The cache manager: pages with a block table per request, in groups, and state slots.
 
 A *group* is a set of layers with the same need: ("paged", None) keeps every key,
-("paged", W) keeps a window of W positions, ("paged", -C) the positions of the current block of C.  Each group has pages of its own (its own pool of
+("paged", W) keeps a window of W positions, ("paged", -C) the positions of the current block of C,
+("paged", (W, K)) a window of W positions beside the sequence's first K, whose pages are never given back.  Each group has pages of its own (its own pool of
 page ids and, per layer of the group, device tensors of its own in the layout its spec chooses:
 [pages, 2, kv heads, page_size, head_dim] for keys and values of one width) and each request has
 one block table per group: entry i is the page that holds
@@ -22,7 +23,7 @@ from dataclasses import dataclass, field
 import torch
 
 from ..errors import CapacityError
-from ..parts.spec import PagedKVSpec, SlotStateSpec, first_reachable
+from ..parts.spec import PagedKVSpec, SlotStateSpec, first_reachable, kept_positions
 from .pages import PagePool, StateSlots
 
 
@@ -102,7 +103,7 @@ class CacheManager:
                     kinds = spec.dtypes or ("compute",) * len(spec.shapes)
                     made.append(tuple(
                         torch.zeros(self.max_seqs + 1, *shape, device=self.device,
-                                    dtype=self.dtype if kind == "compute" else torch.float32)
+                                    dtype={"compute": self.dtype, "i32": torch.int32}.get(kind, torch.float32))
                         for shape, kind in zip(spec.shapes, kinds)))
             self._tensors[idx] = tuple(made)
 
@@ -149,6 +150,10 @@ class CacheManager:
         """First table entry that a query at position >= from_token can still reach."""
         return first_reachable(key[1], from_token) // self.page_size
 
+    def _kept_pages(self, key) -> int:
+        """Table entries at the sequence's start that stay reachable whatever the window."""
+        return pages_for(kept_positions(key[1]), self.page_size)
+
     def missing_pages(self, rc: RequestCache, total_tokens: int) -> dict:
         """{group key -> pages still to take} so that positions [num_tokens, total_tokens) fit."""
         need = {}
@@ -160,8 +165,9 @@ class CacheManager:
                 need[key] = max(0, want - have)
                 continue
             first = self._first_needed_page(key, rc.num_tokens)
-            # entries below `first` are never needed again; entries [have, want) are new
-            need[key] = max(0, want - max(have, first)) + sum(
+            kept = min(self._kept_pages(key), first)
+            # entries below `first` are never needed again, but for the kept ones; entries [have, want) are new
+            need[key] = max(0, want - max(have, first)) + max(0, min(kept, want) - have) + sum(
                 1 for i in range(first, min(have, want)) if table[i] < 0)
         return need
 
@@ -186,8 +192,9 @@ class CacheManager:
             table = rc.tables[key]
             if key[1] is not None:
                 first = self._first_needed_page(key, rc.num_tokens)
-                while len(table) < min(first, want):
-                    table.append(-1)                   # positions a window has passed already
+                kept = self._kept_pages(key)
+                while len(table) < min(first, want):   # positions a window has passed already, but for the kept ones
+                    table.append(pool.alloc(1)[0] if len(table) < kept else -1)
                 for i in range(first, min(len(table), want)):
                     if table[i] < 0:
                         table[i] = pool.alloc(1)[0]
@@ -206,7 +213,7 @@ class CacheManager:
             if key[1] is None:
                 continue
             table = rc.tables[key]
-            for i in range(min(self._first_needed_page(key, total_tokens), len(table))):
+            for i in range(self._kept_pages(key), min(self._first_needed_page(key, total_tokens), len(table))):
                 if table[i] >= 0:
                     pool.release([table[i]])
                     table[i] = -1

@@ -45,7 +45,7 @@ def resolve(names) -> Architecture:
 
 
 def _load_builtin() -> None:
-    from ..models import beledra, lfm2, toderax, zafopel  # noqa: F401  (they register themselves on import)
+    from ..models import beledra, kuzupel, lfm2, toderax, zafopel  # noqa: F401  (they register themselves on import)
 
 
 def architecture_names(raw: dict, cfg: dict | None = None):

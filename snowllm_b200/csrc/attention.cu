@@ -223,14 +223,14 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, T* __restrict__ out, int nh,
                                        int hd, int window, int chunk, int num_chunks,
-                                       const int* __restrict__ row_list) {
+                                       const int* __restrict__ row_list, int keep,
+                                       const T* __restrict__ gate, long long gate_ld) {
   pdl_begin();
   extern __shared__ float merge_sh[];                      // [MERGE_ZG][hd]
   __shared__ float s_mx, s_inv;
   const int m = row_list ? row_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int pos = positions[m];
-  const int lo = first_key(pos, window);
-  const int n = pos / chunk - lo / chunk + 1;              // chunks this row really has
+  const int n = row_chunks(pos, window, keep, chunk);      // chunks this row really has
   const size_t base = ((size_t)blockIdx.x * nh + head) * num_chunks;
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
@@ -243,7 +243,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     if (lane == 0) { s_mx = mx; s_inv = 1.f / l; }
   }
   __syncthreads();
-  const float mx = s_mx, inv = s_inv;
+  // `gate`: the head's output times sigmoid of its own logit, gate[m * gate_ld + head]
+  const float mx = s_mx, inv = gate ? s_inv / (1.f + expf(-to_f<T>(gate[(size_t)m * gate_ld + head]))) : s_inv;
   const int dthreads = blockDim.x / MERGE_ZG, zg = threadIdx.x / dthreads, dt = threadIdx.x % dthreads;
   const int per = (n + MERGE_ZG - 1) / MERGE_ZG;
   const int z0 = min(n, zg * per), z1 = min(n, z0 + per);
@@ -315,7 +316,7 @@ SNK_API int snk_paged_attention_rows(const void* q, const void* pool, const int*
     SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads),
                                    (size_t)MERGE_ZG * hd * sizeof(float), stream, 
                             part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window,
-                            chunk, num_chunks, row_list));
+                            chunk, num_chunks, row_list, 0, static_cast<const T*>(nullptr), 0LL));
     SNK_LAUNCH_CHECK();
   }
   return 0;
@@ -334,7 +335,25 @@ SNK_API int snk_attention_merge(const void* scratch, const int* positions, void*
   SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads),
                                  (size_t)MERGE_ZG * hd * sizeof(float), stream, 
                           part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window, chunk, num_chunks,
-                          row_list));
+                          row_list, 0, static_cast<const T*>(nullptr), 0LL));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// The merge for rows with kept first keys (their chunks as chunk_keys counts them) and a gate per head:
+// gate (may be null) points at the first head's logit of row 0, in the output's dtype, row pitch gate_ld.
+SNK_API int snk_attention_merge_gated(const void* scratch, const int* positions, void* out, int M, int nh, int hd,
+                                      int window, int keep, int chunk, int num_chunks, const void* gate,
+                                      long long gate_ld, int dtype, cudaStream_t stream) {
+  if (M <= 0 || num_chunks <= 1) return 0;
+  const float* part_o = static_cast<const float*>(scratch);
+  const float* part_ml = part_o + (size_t)M * nh * num_chunks * hd;
+  dim3 mgrid(M, nh);
+  const int threads = MERGE_ZG * (hd <= 32 ? 32 : (hd <= 64 ? 64 : 128));
+  SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads),
+                                 (size_t)MERGE_ZG * hd * sizeof(float), stream,
+                                 part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window, chunk, num_chunks,
+                                 static_cast<const int*>(nullptr), keep, static_cast<const T*>(gate), gate_ld));
   SNK_LAUNCH_CHECK();
   return 0;
 }

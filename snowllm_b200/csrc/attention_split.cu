@@ -9,6 +9,9 @@
 //   * `window` > 0: the last `window` keys; < 0: the keys of the query's own block of -window positions
 //     (blocks counted from position 0); a factor per query head on the scale; a sink per query head (one
 //     more term exp(sink) in the softmax's sum, without a key or a value);
+//   * `keep` > 0: beside its window a query reaches the positions below `keep` (the sequence's first tokens);
+//   * bias_len < 0: `bias` holds one slope per query head and slope * (i - j) is taken off the scaled score;
+//   * `gate`: a logit per (row, query head); the head's output is multiplied by its sigmoid;
 //   * scores, softmax weights and the products with the values in float whatever the cache dtype (the
 //     weights are never rounded to 16 bits), output in float or in the compute dtype.
 //
@@ -100,7 +103,22 @@ __global__ void split_prepare_kernel(const T* __restrict__ proj, long long ld, i
     xs[d] = v;
     ss = fmaf(v, v, ss);
   }
-  if (has_norm) {
+  if (has_norm == 2) {
+    // one root mean square over ALL heads of q (or of k): every warp of the row forms the same sum in the
+    // same order; the weight has the projection's size
+    const int n = (is_q ? nq : nkh) * dk;
+    const T* all = row + (is_q ? q_off : k_off);
+    const float* ball = proj_bias ? proj_bias + (is_q ? q_off : k_off) : nullptr;
+    float sa = 0.f;
+    for (int d = lane; d < n; d += 32) {
+      const float v = to_f<T>(all[d]) + (ball ? ball[d] : 0.f);
+      sa = fmaf(v, v, sa);
+    }
+    sa = warp_sum(sa);
+    const float inv = 1.f / sqrtf(sa / (float)n + eps);
+    const SmallVec& g = is_q ? q_gamma : k_gamma;
+    for (int d = lane; d < dk; d += 32) xs[d] = xs[d] * inv * (g.p ? g[(size_t)h * dk + d] : 1.f);
+  } else if (has_norm) {
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / (float)dk + eps);
     const SmallVec& g = is_q ? q_gamma : k_gamma;
@@ -167,7 +185,8 @@ __global__ void split_attention_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, void* __restrict__ out, int out_f32,
     int nq, int nkv, int maps, int dk, int dv, int window, float scale, const float* __restrict__ bias,
-    int bias_len, const float* __restrict__ head_scale, const float* __restrict__ sink, int vec_ok, int chunk,
+    int bias_len, const float* __restrict__ head_scale, const float* __restrict__ sink, int keep,
+    const T* __restrict__ gate, long long gate_ld, int vec_ok, int chunk,
     int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
@@ -184,10 +203,11 @@ __global__ void split_attention_kernel(
   if (num_chunks > 1) {
     // single rows with their keys cut into chunks aligned to absolute positions: this block takes one
     // chunk and leaves (o, max, sum) for the merge (attention.cu), which adds the chunks in order
-    const int cnk = lo / chunk + (int)blockIdx.z;
-    if ((long long)cnk * chunk > hi) return;
-    lo = max(lo, cnk * chunk);
-    hi = min(hi, (cnk + 1) * chunk - 1);
+    int base;
+    bool inside;
+    if (!chunk_keys(pos0, window, keep, chunk, (int)blockIdx.z, lo, hi, base, inside)) return;
+    if (!inside) window = 0;                             // a chunk of kept keys: the row reaches all of it
+    keep = 0;
   }
   const int kw = maps * dk;                              // a key row holds the maps side by side
 
@@ -204,11 +224,14 @@ __global__ void split_attention_kernel(
   }
   const int* bt = block_table + (size_t)row_seg[m0] * max_pages;
   const int t_first = (lo / SA_TILE) * SA_TILE;
-  const int ntiles = (hi - t_first) / SA_TILE + 1;
+  // kept first keys that lie before the walk's first tile come in tiles of their own, ahead of it
+  const int nkeep = keep > 0 ? min((keep + SA_TILE - 1) / SA_TILE, t_first / SA_TILE) : 0;
+  const int ntiles = nkeep + (hi - t_first) / SA_TILE + 1;
+  auto tile_start = [&](int tile) { return tile < nkeep ? tile * SA_TILE : t_first + (tile - nkeep) * SA_TILE; };
 
   auto issue = [&](int tile) {
     if (tile < ntiles) {
-      const int t0 = t_first + tile * SA_TILE;
+      const int t0 = tile_start(tile);
       unsigned char* ks = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
       unsigned char* vs = ks + SA_TILE * k_stride;
       if (vec_ok) {
@@ -216,7 +239,7 @@ __global__ void split_attention_kernel(
         for (int v = threadIdx.x; v < SA_TILE * per; v += blockDim.x) {
           const int j = v / per, c = v - j * per;
           const int kp = t0 + j;
-          const bool valid = kp >= lo && kp <= hi;
+          const bool valid = kp <= hi && (kp >= lo || kp < keep);
           const T* src = kpool;
           unsigned char* dst = c < kv_ ? ks + j * k_stride + c * 16 : vs + j * v_stride + (c - kv_) * 16;
           if (valid) {
@@ -231,7 +254,7 @@ __global__ void split_attention_kernel(
           const int j = v / per, c = v - j * per;
           const int kp = t0 + j;
           T val = from_f<T>(0.f);
-          if (kp >= lo && kp <= hi) {
+          if (kp <= hi && (kp >= lo || kp < keep)) {
             const size_t slot = ((size_t)bt[kp / page_size] * nkv + kvh) * page_size + kp % page_size;
             val = c < kw ? kpool[slot * kw + c] : vpool[slot * dv + (c - kw)];
           }
@@ -266,7 +289,7 @@ __global__ void split_attention_kernel(
     sa_cp_async_wait<SA_STAGES - 2>();
     __syncthreads();                                     // the tile is in (and q, the first time round)
     issue(tile + SA_STAGES - 1);
-    const int t0 = t_first + tile * SA_TILE;
+    const int t0 = tile_start(tile);
     const unsigned char* ks = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
     const unsigned char* vs = ks + SA_TILE * k_stride;
     const int kp = t0 + lane;
@@ -279,8 +302,8 @@ __global__ void split_attention_kernel(
       const int p = pos0 + r;
       const int klo = max(lo, first_key(p, window));
       const int khi = min(p, hi);
-      if (t0 > khi || t0 + SA_TILE - 1 < klo) continue;  // none of this unit's keys in the tile
-      const bool valid = kp >= klo && kp <= khi;
+      if (t0 > khi || (t0 + SA_TILE - 1 < klo && t0 >= keep)) continue;  // none of this unit's keys in the tile
+      const bool valid = kp <= khi && (kp >= klo || kp < keep);
       const float* qw = qs + (size_t)u * dk;
       float s = 0.f;
       if (vec_ok && dk % VEC == 0) {
@@ -301,7 +324,9 @@ __global__ void split_attention_kernel(
         const T* kr = reinterpret_cast<const T*>(ks + lane * k_stride) + map * dk;
         for (int d = 0; d < dk; ++d) s = fmaf(qw[d], to_f<T>(kr[d]), s);
       }
-      if (bias && valid) s += bias[(size_t)(kvh * hpv + hh) * bias_len + min(p - kp, bias_len - 1)];
+      if (bias && valid)
+        s = bias_len < 0 ? fmaf(-bias[kvh * hpv + hh], (float)(p - kp), s)
+                         : s + bias[(size_t)(kvh * hpv + hh) * bias_len + min(p - kp, bias_len - 1)];
       s = valid ? s : -INFINITY;
       const float m_new = fmaxf(mx[i], warp_max(s));     // finite: the tile holds a key of this unit
       const float corr = expf(mx[i] - m_new);            // 0 the first time
@@ -340,7 +365,8 @@ __global__ void split_attention_kernel(
       }
       continue;
     }
-    const float inv = 1.f / l[i];
+    float inv = 1.f / l[i];
+    if (gate) inv /= 1.f + expf(-to_f<T>(gate[(size_t)(m0 + r) * gate_ld + kvh * hpv + hh]));
     const size_t at = ((size_t)(m0 + r) * nq + kvh * hpv + hh) * dv;
 #pragma unroll
     for (int e = 0; e < DPL; ++e) {
@@ -398,7 +424,8 @@ __global__ void split_attention_mma_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, void* __restrict__ out, int out_f32,
     int nq, int nkv, int maps, int dk, int dv, int window, float scale, const float* __restrict__ bias,
-    int bias_len, const float* __restrict__ head_scale, const float* __restrict__ sink, int chunk, int num_chunks,
+    int bias_len, const float* __restrict__ head_scale, const float* __restrict__ sink, int keep,
+    const bf16* __restrict__ gate, long long gate_ld, int chunk, int num_chunks,
     float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
@@ -411,10 +438,11 @@ __global__ void split_attention_mma_kernel(
   int lo = first_key(pos0, window);
   int hi = pos0 + rows - 1;
   if (num_chunks > 1) {
-    const int cnk = lo / chunk + (int)blockIdx.z;
-    if ((long long)cnk * chunk > hi) return;
-    lo = max(lo, cnk * chunk);
-    hi = min(hi, (cnk + 1) * chunk - 1);
+    int base;
+    bool inside;
+    if (!chunk_keys(pos0, window, keep, chunk, (int)blockIdx.z, lo, hi, base, inside)) return;
+    if (!inside) window = 0;                               // a chunk of kept keys: the row reaches all of it
+    keep = 0;
   }
   const int kw = maps * dk;
   const float scale2 = scale * 1.4426950408889634f;
@@ -457,7 +485,10 @@ __global__ void split_attention_mma_kernel(
 
   const int* bt = block_table + (size_t)row_seg[m0] * max_pages;
   const int t_first = (lo / SA_TILE) * SA_TILE;
-  const int ntiles = (hi - t_first) / SA_TILE + 1;
+  // kept first keys that lie before the walk's first tile come in tiles of their own, ahead of it
+  const int nkeep = keep > 0 ? min((keep + SA_TILE - 1) / SA_TILE, t_first / SA_TILE) : 0;
+  const int ntiles = nkeep + (hi - t_first) / SA_TILE + 1;
+  auto tile_start = [&](int tile) { return tile < nkeep ? tile * SA_TILE : t_first + (tile - nkeep) * SA_TILE; };
   // which (key of the tile, 16-byte vector of its row) pairs this thread copies: the same for every tile
   const int kv_ = k_bytes / 16, vv_ = v_bytes / 16, per = kv_ + vv_;
   constexpr int COPIES = 6;                                // 32 keys x up to 48 vectors over 32..128 threads
@@ -472,7 +503,7 @@ __global__ void split_attention_mma_kernel(
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   auto copy_one = [&](unsigned char* ks_, unsigned char* vs_, int t0, int j, int c) {
     const int kp = t0 + j;
-    const bool valid = kp >= lo && kp <= hi;
+    const bool valid = kp <= hi && (kp >= lo || kp < keep);
     const bf16* src = kpool;
     unsigned char* dst = c < kv_ ? ks_ + j * k_stride + c * 16 : vs_ + j * v_stride + (c - kv_) * 16;
     if (valid) {
@@ -484,7 +515,7 @@ __global__ void split_attention_mma_kernel(
   };
   auto issue = [&](int tile) {
     if (tile < ntiles) {
-      const int t0 = t_first + tile * SA_TILE;
+      const int t0 = tile_start(tile);
       unsigned char* ks_ = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
       unsigned char* vs_ = ks_ + SA_TILE * k_stride;
 #pragma unroll
@@ -526,14 +557,14 @@ __global__ void split_attention_mma_kernel(
     sa_cp_async_wait<SA_STAGES - 2>();
     __syncthreads();
     issue(tile + SA_STAGES - 1);
-    const int t0 = t_first + tile * SA_TILE;
+    const int t0 = tile_start(tile);
     // the warp's slots span positions pos0 + first slot / G .. ; skip tiles none of them reaches
     if (!warp_live) continue;
     {
       const int s_lo = (warp / maps) * 16, s_hi = min(slots - 1, s_lo + 15);
       const int p_lo = pos0 + s_lo / G, p_hi = pos0 + s_hi / G;
       const int w_lo = max(lo, first_key(p_lo, window)), w_hi = min(p_hi, hi);
-      if (t0 > w_hi || t0 + SA_TILE - 1 < w_lo) continue;
+      if (t0 > w_hi || (t0 + SA_TILE - 1 < w_lo && t0 >= keep)) continue;
     }
     const unsigned char* ks_ = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
     const unsigned char* vs_ = ks_ + SA_TILE * k_stride;
@@ -559,8 +590,8 @@ __global__ void split_attention_mma_kernel(
     float tmax[2] = {-INFINITY, -INFINITY};
     const bool inner = t0 >= max(klo[0], klo[1]) && t0 + SA_TILE - 1 <= min(khi[0], khi[1]);   // no key is masked
     if (inner) {
-      const float* brow[2] = {bias ? bias + (size_t)head[0] * bias_len : nullptr,
-                              bias ? bias + (size_t)head[1] * bias_len : nullptr};
+      const float* brow[2] = {bias && bias_len > 0 ? bias + (size_t)head[0] * bias_len : nullptr,
+                              bias && bias_len > 0 ? bias + (size_t)head[1] * bias_len : nullptr};
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
@@ -569,7 +600,8 @@ __global__ void split_attention_mma_kernel(
           float s = sc[nt][e] * scale2h[h2];
           if (bias) {
             const int dist = p_row[h2] - (t0 + nt * 8 + tq * 2 + (e & 1));
-            s = fmaf(brow[h2][min(dist, bias_len - 1)], 1.4426950408889634f, s);
+            s = bias_len < 0 ? fmaf(-bias[head[h2]] * (float)dist, 1.4426950408889634f, s)
+                             : fmaf(brow[h2][min(dist, bias_len - 1)], 1.4426950408889634f, s);
           }
           sc[nt][e] = s;
           tmax[h2] = fmaxf(tmax[h2], s);
@@ -583,9 +615,11 @@ __global__ void split_attention_mma_kernel(
           const int h2 = e >> 1;
           const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
           float s = sc[nt][e] * scale2h[h2];
-          const bool valid = kp >= klo[h2] && kp <= khi[h2];
+          const bool valid = kp <= khi[h2] && (kp >= klo[h2] || kp < keep);
           if (bias && valid)
-            s = fmaf(bias[(size_t)head[h2] * bias_len + min(p_row[h2] - kp, bias_len - 1)], 1.4426950408889634f, s);
+            s = bias_len < 0 ? fmaf(-bias[head[h2]] * (float)(p_row[h2] - kp), 1.4426950408889634f, s)
+                             : fmaf(bias[(size_t)head[h2] * bias_len + min(p_row[h2] - kp, bias_len - 1)],
+                                    1.4426950408889634f, s);
           s = valid ? s : -INFINITY;
           sc[nt][e] = s;
           tmax[h2] = fmaxf(tmax[h2], s);
@@ -676,7 +710,8 @@ __global__ void split_attention_mma_kernel(
       }
       continue;
     }
-    const float inv = 1.f / l[h2];
+    float inv = 1.f / l[h2];
+    if (gate) inv /= 1.f + expf(-__bfloat162float(gate[(size_t)(m0 + r) * gate_ld + head[h2]]));
     const size_t at = ((size_t)(m0 + r) * nq + head[h2]) * dv;
 #pragma unroll
     for (int nt = 0; nt < DVT; ++nt) {
@@ -710,7 +745,8 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
                         const int* __restrict__ positions, const int* __restrict__ row_seg,
                         void* __restrict__ out, int out_f32, int nq, int nkv, int maps, int dk, int dv, int window,
                         float scale, const float* __restrict__ bias, int bias_len,
-                        const float* __restrict__ head_scale, const float* __restrict__ sink, int num_chunks,
+                        const float* __restrict__ head_scale, const float* __restrict__ sink, int keep,
+                        const bf16* __restrict__ gate, long long gate_ld, int num_chunks,
                         float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
@@ -719,11 +755,9 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
   const int m = blockIdx.x, kvh = blockIdx.y;
   const int hpv = nq / nkv, G = hpv / maps;
   const int pos = positions[m];
-  const int lo_row = first_key(pos, window);
-  const int cnk = lo_row / SD_CHUNK + (int)blockIdx.z;
-  if ((long long)cnk * SD_CHUNK > pos) return;
-  const int c0 = cnk * SD_CHUNK;
-  const int lo = max(lo_row, c0), hi = min(pos, c0 + SD_CHUNK - 1);
+  int lo, hi, c0;
+  bool inside;
+  if (!chunk_keys(pos, window, keep, SD_CHUNK, (int)blockIdx.z, lo, hi, c0, inside)) return;
   const int kw = maps * dk;
   const float scale2 = scale * 1.4426950408889634f;
   const int k_bytes = kw * 2, v_bytes = dv * 2;
@@ -811,7 +845,9 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
           float sv = sc[nt][e] * (head_scale ? scale2 * head_scale[head[h2]] : scale2);
           const bool valid = live[h2] && kp >= lo && kp <= hi;
           if (bias && valid)
-            sv = fmaf(bias[(size_t)head[h2] * bias_len + min(pos - kp, bias_len - 1)], 1.4426950408889634f, sv);
+            sv = bias_len < 0 ? fmaf(-bias[head[h2]] * (float)(pos - kp), 1.4426950408889634f, sv)
+                              : fmaf(bias[(size_t)head[h2] * bias_len + min(pos - kp, bias_len - 1)],
+                                     1.4426950408889634f, sv);
           sv = valid ? sv : -INFINITY;
           sc[nt][e] = sv;
           mrow[h2] = fmaxf(mrow[h2], sv);
@@ -916,7 +952,8 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
         part_ml[slot * 2 + 1] = l;
       }
     } else {
-      const float v = acc / l;
+      float v = acc / l;
+      if (gate) v /= 1.f + expf(-__bfloat162float(gate[(size_t)m * gate_ld + head]));
       const size_t at = ((size_t)m * nq + head) * dv + d;
       if (out_f32) static_cast<float*>(out)[at] = v;
       else static_cast<bf16*>(out)[at] = __float2bfloat16_rn(v);
@@ -965,14 +1002,16 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
                                 int max_pages, int page_size, const int* positions, const int* row_seg,
                                 const int* tiles, int num_tiles, int tile_rows, void* out, int out_f32, int nq,
                                 int nkv, int maps, int dk, int dv, int window, float scale, const float* bias,
-                                int bias_len, const float* head_scale, const float* sink, int chunk,
+                                int bias_len, const float* head_scale, const float* sink, int keep,
+                                const void* gate, long long gate_ld, int chunk,
                                 int num_chunks, void* scratch, int dtype, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nkv <= 0 || maps <= 0 || nq % (nkv * maps) || dk <= 0 || dv <= 0 || dv > 256) return SNK_ERR_SIZE;
   const int hpv = nq / nkv;
   if (tile_rows < 1 || nkv > 65535) return SNK_ERR_SIZE;
   if (!tiles) tile_rows = 1;
-  if (bias && bias_len <= 0) return SNK_ERR_SIZE;
+  if (bias && bias_len == 0) return SNK_ERR_SIZE;
+  if (keep < 0 || (keep > 0 && window <= 0)) return SNK_ERR_SIZE;     // kept first keys go with a sliding window
   if (num_chunks < 1 || num_chunks > 65535) return SNK_ERR_SIZE;
   if (num_chunks > 1 && (tiles || scratch == nullptr || chunk <= 0 || chunk % SA_TILE)) return SNK_ERR_SIZE;
   float* part_o = static_cast<float*>(scratch);
@@ -992,7 +1031,8 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_decode_mma_kernel<DKS_, DVT_>, dim3(grid), dim3(SD_WARPS * 32), smem, stream,           \
                static_cast<const bf16*>(q), static_cast<const bf16*>(kpool), static_cast<const bf16*>(vpool), \
                block_table, max_pages, page_size, positions, row_seg, out, out_f32, nq, nkv, maps, dk, dv,   \
-               window, scale, bias, bias_len, head_scale, sink, num_chunks, part_o, part_ml);                                  \
+               window, scale, bias, bias_len, head_scale, sink, keep, static_cast<const bf16*>(gate), gate_ld,   \
+               num_chunks, part_o, part_ml);                                                                 \
   } while (0)
     if (dk <= 64 && dv <= 64) SD_MMA(4, 8);
     else if (dk <= 64) SD_MMA(4, 16);
@@ -1020,7 +1060,8 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_attention_mma_kernel<DKS_, DVT_>, dim3(grid), dim3(warps * 32), smem, stream,           \
                static_cast<const bf16*>(q), static_cast<const bf16*>(kpool), static_cast<const bf16*>(vpool), \
                block_table, max_pages, page_size, positions, row_seg, tiles, out, out_f32, nq, nkv, maps,    \
-               dk, dv, window, scale, bias, bias_len, head_scale, sink, chunk, num_chunks, part_o, part_ml);                   \
+               dk, dv, window, scale, bias, bias_len, head_scale, sink, keep, static_cast<const bf16*>(gate),    \
+               gate_ld, chunk, num_chunks, part_o, part_ml);                                                 \
   } while (0)
     if (dk <= 64 && dv <= 64) SA_MMA(4, 8);
     else if (dk <= 64) SA_MMA(4, 16);
@@ -1050,8 +1091,8 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_attention_kernel<T, DPL_, UPW_>, dim3(grid), dim3(warps * 32), smem, stream,      \
                static_cast<const T*>(q), static_cast<const T*>(kpool), static_cast<const T*>(vpool),   \
                block_table, max_pages, page_size, positions, row_seg, tiles, out, out_f32, nq, nkv,    \
-               maps, dk, dv, window, scale, bias, bias_len, head_scale, sink, vec_ok, chunk, num_chunks,  \
-               part_o, part_ml);                                                                        \
+               maps, dk, dv, window, scale, bias, bias_len, head_scale, sink, keep,                    \
+               static_cast<const T*>(gate), gate_ld, vec_ok, chunk, num_chunks, part_o, part_ml);      \
   } while (0)
 #define SA_LAUNCH_U(DPL_)                  \
   do {                                     \

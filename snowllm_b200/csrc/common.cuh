@@ -85,6 +85,41 @@ __host__ __device__ __forceinline__ int first_key(int pos, int window) {
   if (window < 0) return pos - pos % (-window);
   return 0;
 }
+// Kept first keys.  With `keep` > 0 a query also reaches positions below `keep` that lie before its window
+// (a window that slides, and the sequence's first tokens beside it).  Where a row's keys are cut into chunks of
+// `chunk` keys, its kept keys [0, min(keep, first_key)) come first, in chunks counted from position 0, and the
+// chunks of its window follow, counted from first_key / chunk: chunk z of the row holds the keys [lo, hi] of
+// which the first lies in the tile-aligned run that starts at `base`.  False: the row has no chunk z.
+// `inside` says whether the window still masks within the chunk (a chunk of kept keys is reached whole).
+__host__ __device__ __forceinline__ int kept_chunks(int pos, int window, int keep, int chunk) {
+  if (keep <= 0) return 0;
+  const int lo = first_key(pos, window);
+  const int end = keep < lo ? keep : lo;
+  return (end + chunk - 1) / chunk;
+}
+__host__ __device__ __forceinline__ bool chunk_keys(int pos, int window, int keep, int chunk, int z, int& lo,
+                                                    int& hi, int& base, bool& inside) {
+  const int lo_row = first_key(pos, window);
+  const int nk = kept_chunks(pos, window, keep, chunk);
+  if (z < nk) {
+    const int end = keep < lo_row ? keep : lo_row;
+    base = lo = z * chunk;
+    hi = (z + 1) * chunk < end ? (z + 1) * chunk - 1 : end - 1;
+    inside = false;
+    return true;
+  }
+  const long long cnk = (long long)(lo_row / chunk) + (z - nk);
+  if (cnk * chunk > pos) return false;
+  base = (int)cnk * chunk;
+  lo = lo_row > base ? lo_row : base;
+  hi = pos < base + chunk - 1 ? pos : base + chunk - 1;
+  inside = true;
+  return true;
+}
+// Chunks that a row at `pos` really has under chunk_keys.
+__host__ __device__ __forceinline__ int row_chunks(int pos, int window, int keep, int chunk) {
+  return kept_chunks(pos, window, keep, chunk) + pos / chunk - first_key(pos, window) / chunk + 1;
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -35,6 +35,77 @@ SNK_API int snk_embedding(const int* ids, const int* pending, int num_pending, c
   return 0;
 }
 
+// The embedding with a second table read by a hash of the token and the one before it:
+//   h[m,:] = E[id,:] * scale + P[(prev * mul_prev + id * mul_cur) mod buckets, :],
+// and a sequence's first token, which has no token before it, reads row `buckets` of P (the table's last
+// row).  The token before a step's first token is the request's state: last_token[slot] (ignored when the
+// request starts at position 0).  The block of a segment's first row reads that state and then writes the
+// segment's last token into it, so the read and the write are one block's, in that order.
+template <typename T>
+__global__ void pair_embedding_kernel(const int* __restrict__ ids, const int* __restrict__ pending, int num_pending,
+                                      const T* __restrict__ table, const T* __restrict__ pairs,
+                                      float* __restrict__ out, int H, int V, float scale, long long buckets,
+                                      long long mul_prev, long long mul_cur, const int* __restrict__ row_seg,
+                                      const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
+                                      const int* __restrict__ seg_slot, int* __restrict__ last_token) {
+  pdl_begin();
+  const int m = blockIdx.x;
+  auto token = [&](int row) {
+    int id = ids[row];
+    if (id < 0 && pending != nullptr && -(id + 1) < num_pending) id = pending[-(id + 1)];
+    return id;
+  };
+  const int id = token(m);
+  const int seg = row_seg[m];
+  const int first = cu_seqlens[seg];
+  int prev = -1;                                     // none: the sequence's first token
+  if (m > first) {
+    prev = token(m - 1);
+  } else {
+    if (seg_start[seg] > 0) prev = last_token[seg_slot[seg]];
+    __syncthreads();                                 // every thread has read the state before one rewrites it
+    if (threadIdx.x == 0) last_token[seg_slot[seg]] = token(cu_seqlens[seg + 1] - 1);
+  }
+  const bool ok = id >= 0 && id < V;                 // the host checks ids; a bad one reads nothing
+  const long long pr = prev >= 0 ? ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets : buckets;
+  const T* row = table + (size_t)(ok ? id : 0) * H;
+  const T* prow = pairs + (size_t)(ok ? pr : 0) * H;
+  float* o = out + (size_t)m * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    o[i] = ok ? fmaf(to_f<T>(row[i]), scale, to_f<T>(prow[i])) : 0.f;
+}
+
+SNK_API int snk_pair_embedding(const int* ids, const int* pending, int num_pending, const void* table,
+                               const void* pairs, float* out, int M, int H, int V, int dtype, float scale,
+                               long long buckets, long long mul_prev, long long mul_cur, const int* row_seg,
+                               const int* cu_seqlens, const int* seg_start, const int* seg_slot, int* last_token,
+                               cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (buckets <= 0 || mul_prev < 0 || mul_cur < 0) return SNK_ERR_SIZE;
+  const int threads = H >= 1024 ? 256 : 128;
+  SNK_DISPATCH(dtype, snk_launch(pair_embedding_kernel<T>, dim3(M), dim3(threads), 0, stream, ids, pending,
+                                 num_pending, static_cast<const T*>(table), static_cast<const T*>(pairs), out, H, V,
+                                 scale, buckets, mul_prev, mul_cur, row_seg, cu_seqlens, seg_start, seg_slot,
+                                 last_token));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// logits <- cap * tanh(logits / cap), in place, float.
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+  pdl_begin();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+SNK_API int snk_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.f)) return SNK_ERR_SIZE;
+  snk_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, (size_t)n, cap);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // One block per output row.  rows == nullptr: row r is residual row r; delta (if any) is
 // added into the residual and the sum is written back.  rows != nullptr: output row r
@@ -44,7 +115,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
                                    SmallVec gamma, T* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps, int vec4,
                                    const float* __restrict__ moe_y, const int* __restrict__ pair_pos,
-                                   const float* __restrict__ topk_w, int k) {
+                                   const float* __restrict__ topk_w, int k, float dscale,
+                                   const float* __restrict__ dgate, int dgate_ld) {
   pdl_begin();
   extern __shared__ __align__(16) float xs[];   // H floats + 33 for the reduction
   float* red = xs + ((H + 3) & ~3);
@@ -52,46 +124,35 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* res = residual + src * H;
   const float* d = delta ? delta + src * H : nullptr;
+  // what is added: dscale * (g * delta + the routed experts' weighted sum), g = sigmoid(dgate[row]) or 1
+  const float g = dgate ? 1.f / (1.f + expf(-dgate[src * dgate_ld])) : 1.f;
   float ss = 0.f;
   T* o = out + (size_t)r * H;
-  if (moe_y) {
-    // The delta is the routed experts' weighted sum, formed here instead of by a kernel of its own:
-    // sum_j w[src, j] * y[pair_pos[src*k + j], :], j in order (the rows are 16-byte aligned).
-    float4* xs4 = reinterpret_cast<float4*>(xs);
-    float4* res4 = reinterpret_cast<float4*>(res);
-    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int j = 0; j < k; ++j) {
-        const float w = topk_w[src * k + j];
-        const float4 y = reinterpret_cast<const float4*>(moe_y + (size_t)pair_pos[src * k + j] * H)[i];
-        acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
-        acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
-      }
-      float4 v = res4[i];
-      v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
-      if (!rows) res4[i] = v;
-      xs4[i] = v;
-      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);      // one fixed order of the squares in every path
-      ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-    }
-    ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-      const float4 v = xs4[i];
-      store4<T>(o + 4 * i, v.x * inv * gamma[4 * i], v.y * inv * gamma[4 * i + 1], v.z * inv * gamma[4 * i + 2],
-                v.w * inv * gamma[4 * i + 3]);
-    }
-    return;
-  }
   if (vec4) {                                   // H a multiple of 4 and 16-byte aligned rows
     float4* xs4 = reinterpret_cast<float4*>(xs);
     float4* res4 = reinterpret_cast<float4*>(res);
     const float4* d4 = reinterpret_cast<const float4*>(d);
     for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-      float4 v = res4[i];
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (moe_y) {
+        // The routed experts' weighted sum, formed here instead of by a kernel of its own:
+        // sum_j w[src, j] * y[pair_pos[src*k + j], :], j in order (the rows are 16-byte aligned).
+        for (int j = 0; j < k; ++j) {
+          const float w = topk_w[src * k + j];
+          const float4 y = reinterpret_cast<const float4*>(moe_y + (size_t)pair_pos[src * k + j] * H)[i];
+          acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
+          acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
+        }
+      }
       if (d) {
         const float4 e = d4[i];
-        v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+        acc.x = fmaf(g, e.x, acc.x); acc.y = fmaf(g, e.y, acc.y);
+        acc.z = fmaf(g, e.z, acc.z); acc.w = fmaf(g, e.w, acc.w);
+      }
+      float4 v = res4[i];
+      if (d || moe_y) {
+        v.x = fmaf(dscale, acc.x, v.x); v.y = fmaf(dscale, acc.y, v.y);
+        v.z = fmaf(dscale, acc.z, v.z); v.w = fmaf(dscale, acc.w, v.w);
         if (!rows) res4[i] = v;
       }
       xs4[i] = v;
@@ -110,7 +171,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = res[i];
     if (d) {
-      v += d[i];
+      v = fmaf(dscale, g * d[i], v);
       if (!rows) res[i] = v;
     }
     xs[i] = v;
@@ -139,7 +200,8 @@ template <typename T, int ITERS>
 __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                        SmallVec gamma, T* __restrict__ out, const int* __restrict__ rows,
                                        int H, float eps, const float* __restrict__ moe_y,
-                                       const int* __restrict__ pair_pos, const float* __restrict__ topk_w, int k) {
+                                       const int* __restrict__ pair_pos, const float* __restrict__ topk_w, int k,
+                                       float dscale, const float* __restrict__ dgate, int dgate_ld) {
   pdl_begin();
   __shared__ float red[33];
   const int r = blockIdx.x, n4 = H / 4;
@@ -151,11 +213,11 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const float
     const int i = threadIdx.x + it * blockDim.x;
     v[it] = i < n4 ? res4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  float4 acc[ITERS];                                        // what is added, before dscale
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) acc[it] = make_float4(0.f, 0.f, 0.f, 0.f);
   if (moe_y) {
     // the routed experts' weighted sum, j in order, then the residual sum: as the kernel above forms it
-    float4 acc[ITERS];
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) acc[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     constexpr int JU = ITERS <= 2 ? 4 : 2;                  // picks whose rows are in flight together
     for (int j0 = 0; j0 < k; j0 += JU) {
       float w[JU];
@@ -185,11 +247,9 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const float
         }
       }
     }
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      v[it].x += acc[it].x; v[it].y += acc[it].y; v[it].z += acc[it].z; v[it].w += acc[it].w;
-    }
-  } else if (delta) {
+  }
+  if (delta) {
+    const float g = dgate ? 1.f / (1.f + expf(-dgate[src * dgate_ld])) : 1.f;
     const float4* d4 = reinterpret_cast<const float4*>(delta + src * H);
     float4 e[ITERS];
 #pragma unroll
@@ -199,7 +259,15 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const float
     }
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
-      v[it].x += e[it].x; v[it].y += e[it].y; v[it].z += e[it].z; v[it].w += e[it].w;
+      acc[it].x = fmaf(g, e[it].x, acc[it].x); acc[it].y = fmaf(g, e[it].y, acc[it].y);
+      acc[it].z = fmaf(g, e[it].z, acc[it].z); acc[it].w = fmaf(g, e[it].w, acc[it].w);
+    }
+  }
+  if (moe_y || delta) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      v[it].x = fmaf(dscale, acc[it].x, v[it].x); v[it].y = fmaf(dscale, acc[it].y, v[it].y);
+      v[it].z = fmaf(dscale, acc[it].z, v[it].z); v[it].w = fmaf(dscale, acc[it].w, v[it].w);
     }
   }
   float ss = 0.f;
@@ -230,11 +298,13 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const float
   }
 }
 
-// moe_y (may be null): instead of delta, add sum_j topk_w[row, j] * moe_y[pair_pos[row*k + j], :].
+// What is added into the residual: dscale * (g * delta + sum_j topk_w[row, j] * moe_y[pair_pos[row*k + j], :]);
+// delta and moe_y may each be null; g = sigmoid(dgate[row * dgate_ld]) (a gate per row on delta), 1 without.
 SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gamma,
                             int gamma_is_f32, void* out, const int* rows, int R, int H,
                             float eps, int dtype, const float* moe_y, const int* pair_pos,
-                            const float* topk_w, int k, cudaStream_t stream) {
+                            const float* topk_w, int k, float dscale, const float* dgate, int dgate_ld,
+                            cudaStream_t stream) {
   if (R <= 0) return 0;
   if (H <= 0 || H > 65536) return SNK_ERR_SIZE;
   if (moe_y && (H % 4 || (uintptr_t)moe_y % 16 || (uintptr_t)residual % 16 || (uintptr_t)out % 16 || k <= 0))
@@ -255,7 +325,7 @@ SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gam
     const int iters = (H / 4 + reg_threads - 1) / reg_threads;
 #define NORM_REG(I_)                                                                                      \
   snk_launch(add_rmsnorm_reg_kernel<T, I_>, dim3(R), dim3(reg_threads), 0, stream, residual, delta, g,    \
-             static_cast<T*>(out), rows, H, eps, moe_y, pair_pos, topk_w, k)
+             static_cast<T*>(out), rows, H, eps, moe_y, pair_pos, topk_w, k, dscale, dgate, dgate_ld)
     SNK_DISPATCH(dtype, {
       if (iters <= 1) NORM_REG(1);
       else if (iters <= 2) NORM_REG(2);
@@ -272,7 +342,7 @@ SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gam
                            (int)smem);
     snk_launch(add_rmsnorm_kernel<T>, dim3(R), dim3(threads), smem, stream, residual, delta, g,
                                                         static_cast<T*>(out), rows, H, eps, vec4, moe_y, pair_pos,
-                                                        topk_w, k);
+                                                        topk_w, k, dscale, dgate, dgate_ld);
   });
   SNK_LAUNCH_CHECK();
   return 0;

@@ -22,14 +22,32 @@
 // norm_topk is a pair of flags: bit 0 renormalises the picks' weights by their sum; bit 1 says that prob[] and
 // score[] hold the experts' LOGITS and the weights are their softmax over all E experts (exp(z - max) over
 // the sum of all, in float).  The order of the logits is the order of the softmax, ties included.
+// Bit 2: the logits (with the bias, which is then a part of the logit and not only of the selection) are the
+// scores, the k largest are picked, and the weights are the softmax over the PICKED logits alone.
 #define ROUTE_RENORM 1
 #define ROUTE_SOFTMAX 2
+#define ROUTE_PICKED 4
 __device__ __forceinline__ float route_score(float logit, int flags) {
-  return (flags & ROUTE_SOFTMAX) ? logit : 1.f / (1.f + expf(-logit));
+  return (flags & (ROUTE_SOFTMAX | ROUTE_PICKED)) ? logit : 1.f / (1.f + expf(-logit));
+}
+// One expert's logit into prob[] (what the weights are made from) and score[] (what selects).
+__device__ __forceinline__ void route_put(float logit, const float* __restrict__ bias, int e, int flags,
+                                          float* prob, float* score) {
+  if (flags & ROUTE_PICKED) {
+    const float z = bias ? logit + bias[e] : logit;
+    prob[e] = z;
+    score[e] = z;
+    return;
+  }
+  const float p = route_score(logit, flags);
+  prob[e] = p;
+  score[e] = bias ? p + bias[e] : p;
 }
 __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids, float* wts, int E, int k,
                                             int flags, float scaling, int lane) {
-  const int norm_topk = flags & ROUTE_RENORM;
+  const bool picked = (flags & ROUTE_PICKED) != 0;
+  const int norm_topk = (flags & ROUTE_RENORM) || picked;
+  float first = 0.f;             // the largest picked logit: the reference of the picks' softmax
   if (flags & ROUTE_SOFTMAX) {
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
@@ -59,7 +77,11 @@ __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids,
       if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
     }
     if (best_e == 0x7fffffff) best_e = j < E ? j : 0;   // every score NaN: fall back to index order
-    const float p = prob[best_e];
+    float p = prob[best_e];
+    if (picked) {
+      if (j == 0) first = p;
+      p = expf(p - first);
+    }
     wsum += p;
     if (lane == 0) score[best_e] = -INFINITY;
     __syncwarp();
@@ -73,7 +95,7 @@ __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids,
       }
     }
   }
-  const float mul = (norm_topk ? 1.f / (wsum + 1e-6f) : 1.f);
+  const float mul = picked ? 1.f / wsum : (norm_topk ? 1.f / (wsum + 1e-6f) : 1.f);
   if (k <= 32) {                   // one round: every pick is in a lane's registers; written once, normalised
     if (lane < k) {
       ids[lane] = my_id;
@@ -145,9 +167,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const flo
         ? warp_dot<T, float>(xr, static_cast<const float*>(wr.p) + (size_t)e * H, H, lane, vec)
         : warp_dot<T, bf16>(xr, static_cast<const bf16*>(wr.p) + (size_t)e * H, H, lane, vec);
     if (lane == 0) {
-      const float p = route_score(acc, norm_topk);
-      prob[e] = p;
-      score[e] = bias ? p + bias[e] : p;
+      route_put(acc, bias, e, norm_topk, prob, score);
     }
   }
   __syncthreads();
@@ -193,9 +213,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* _
       x += 0.f;                                          // the sum starts from zero, as the product's own sum does
       for (int q = 1; q < planes; ++q) x += logits[(size_t)q * M * E + (size_t)m * E + e];
     }
-    const float p = route_score(x, norm_topk);
-    prob[e] = p;
-    score[e] = bias ? p + bias[e] : p;
+    route_put(x, bias, e, norm_topk, prob, score);
   }
   __syncwarp();
   select_topk(prob, score, topk_ids + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
@@ -331,9 +349,7 @@ __global__ void moe_topk_sort_kernel(const float* __restrict__ logits, const flo
   float* score = prob + E;
   for (int m = warp; m < M; m += nwarp) {
     for (int e = lane; e < E; e += 32) {
-      const float p = route_score(logits[(size_t)m * E + e], norm_topk);
-      prob[e] = p;
-      score[e] = bias ? p + bias[e] : p;
+      route_put(logits[(size_t)m * E + e], bias, e, norm_topk, prob, score);
     }
     __syncwarp();
     select_topk(prob, score, ids_s + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
@@ -523,9 +539,7 @@ norm_route_sort_kernel(float* __restrict__ residual, const float* __restrict__ d
           ? warp_dot_shared<float, false>(xs, static_cast<const float*>(wr.p) + (size_t)e * H, H, lane, vec)
           : warp_dot_shared<bf16, false>(xs, static_cast<const bf16*>(wr.p) + (size_t)e * H, H, lane, vec);
     if (lane == 0) {
-      const float p = route_score(acc, norm_topk);
-      prob[e] = p;
-      score[e] = bias ? p + bias[e] : p;
+      route_put(acc, bias, e, norm_topk, prob, score);
     }
   }
   __syncthreads();

@@ -285,3 +285,123 @@ SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* s
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The plain causal convolution (no gates) over the first C columns of rows u [M, ld]:
+//   y[t, c] = sum_{j<L} w[c, j] * u~[t - (L-1) + j, c],  float accumulation in tap order,
+// where u~ is the request's history (the last L-1 rows of u of earlier steps; zeros for a request that
+// starts at position 0, whatever its slot holds) followed by this step's rows; state <- the last L-1 rows
+// of u~ (oldest first), [slots, L-1, C].  The rows are a projection's output as it was stored, so the
+// history holds the same values that a longer step would read from its own rows: a sequence gives the
+// same bits however it is cut.  Launches as above: one that only reads the state and one that rewrites
+// it; steps of one token per segment do both in one.
+template <typename T>
+__global__ void causal_conv_kernel(const T* __restrict__ u, long long ld, SmallVec w, const T* __restrict__ state,
+                                   const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
+                                   const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
+                                   T* __restrict__ out, long long out_ld, int C, int L) {
+  pdl_begin();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int m = blockIdx.y;
+  const int seg = row_seg[m];
+  const int first = cu_seqlens[seg];
+  const int t = m - first;
+  const bool has_state = seg_start[seg] > 0;
+  const T* st = state + (size_t)seg_slot[seg] * (L - 1) * C;
+  float acc = 0.f;
+#pragma unroll 4
+  for (int j = 0; j < L; ++j) {
+    const int s = t - (L - 1) + j;                   // index into this step's rows; < 0: history
+    float v;
+    if (s >= 0) v = to_f<T>(u[(size_t)(first + s) * ld + c]);
+    else v = has_state ? to_f<T>(st[(size_t)(s + L - 1) * C + c]) : 0.f;
+    acc = fmaf(w[(size_t)c * L + j], v, acc);
+  }
+  out[(size_t)m * out_ld + c] = from_f<T>(acc);
+}
+
+template <typename T>
+__global__ void causal_conv_state_kernel(const T* __restrict__ u, long long ld, T* __restrict__ state,
+                                         const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
+                                         const int* __restrict__ seg_slot, int C, int L) {
+  pdl_begin();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seg = blockIdx.y;
+  const int first = cu_seqlens[seg], n = cu_seqlens[seg + 1] - first;
+  if (n <= 0) return;
+  const bool has_state = seg_start[seg] > 0;
+  T* st = state + (size_t)seg_slot[seg] * (L - 1) * C;
+  T next[CONV_MAX_L];
+  // history ++ rows has L-1+n rows; the new state is rows n .. n+L-2 of it
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_L; ++i) {
+    if (i < L - 1) {
+      const int idx = n + i;
+      if (idx < L - 1) next[i] = has_state ? st[(size_t)idx * C + c] : from_f<T>(0.f);
+      else next[i] = u[(size_t)(first + idx - (L - 1)) * ld + c];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_L; ++i)
+    if (i < L - 1) st[(size_t)i * C + c] = next[i];
+}
+
+template <typename T>
+__global__ void causal_conv_decode_kernel(const T* __restrict__ u, long long ld, SmallVec w, T* __restrict__ state,
+                                          const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                                          T* __restrict__ out, long long out_ld, int C, int L) {
+  pdl_begin();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seg = blockIdx.y;                        // = the row: one token per segment
+  const bool has_state = seg_start[seg] > 0;
+  T* st = state + (size_t)seg_slot[seg] * (L - 1) * C;
+  T hist[CONV_MAX_L];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j)
+    if (j < L - 1) hist[j] = has_state ? st[(size_t)j * C + c] : from_f<T>(0.f);
+  const T cur = u[(size_t)seg * ld + c];
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j)
+    if (j < L - 1) acc = fmaf(w[(size_t)c * L + j], to_f<T>(hist[j]), acc);
+  acc = fmaf(w[(size_t)c * L + L - 1], to_f<T>(cur), acc);
+  out[(size_t)seg * out_ld + c] = from_f<T>(acc);
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j)
+    if (j < L - 1) st[(size_t)j * C + c] = j + 1 < L - 1 ? hist[j + 1] : cur;
+}
+
+SNK_API int snk_causal_conv(const void* u, long long ld, const void* w, int w_is_f32, void* state,
+                            const int* cu_seqlens, const int* seg_start, const int* seg_slot, const int* row_seg,
+                            void* out, long long out_ld, int M, int B, int C, int L, int dtype,
+                            cudaStream_t stream) {
+  if (M <= 0 || B <= 0 || C <= 0) return 0;
+  if (L < 1 || L > CONV_MAX_L || M > 65535 * 64 || B > 65535) return SNK_ERR_SIZE;
+  const int threads = 128;
+  SmallVec wv{w, w_is_f32};
+  if (M == B && L > 1) {                             // one token per segment
+    dim3 dgrid((C + threads - 1) / threads, B);
+    SNK_DISPATCH(dtype, snk_launch(causal_conv_decode_kernel<T>, dim3(dgrid), dim3(threads), 0, stream,
+                                   static_cast<const T*>(u), ld, wv, static_cast<T*>(state), seg_start, seg_slot,
+                                   static_cast<T*>(out), out_ld, C, L));
+    SNK_LAUNCH_CHECK();
+    return 0;
+  }
+  if (M > 65535) return SNK_ERR_SIZE;
+  dim3 grid((C + threads - 1) / threads, M);
+  SNK_DISPATCH(dtype, snk_launch(causal_conv_kernel<T>, dim3(grid), dim3(threads), 0, stream,
+                                 static_cast<const T*>(u), ld, wv, static_cast<const T*>(state), cu_seqlens,
+                                 seg_start, seg_slot, row_seg, static_cast<T*>(out), out_ld, C, L));
+  SNK_LAUNCH_CHECK();
+  if (L > 1) {
+    dim3 sgrid((C + threads - 1) / threads, B);
+    SNK_DISPATCH(dtype, snk_launch(causal_conv_state_kernel<T>, dim3(sgrid), dim3(threads), 0, stream,
+                                   static_cast<const T*>(u), ld, static_cast<T*>(state), cu_seqlens, seg_start,
+                                   seg_slot, C, L));
+    SNK_LAUNCH_CHECK();
+  }
+  return 0;
+}

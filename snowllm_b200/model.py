@@ -95,9 +95,15 @@ class Model:
             self.head.bind({"weight": self.embedding.weight})
         self.bound = True
 
+    EMBEDDING_CACHE = "embedding"      # the key of an embedding's own state among the cache specs
+
     def cache_specs(self) -> dict:
-        """{run entry index -> cache spec} for the entries that own a cache."""
+        """{run entry index -> cache spec} for the entries that own a cache; an embedding that keeps state
+        per request (the token before a step's first) adds its spec under ``EMBEDDING_CACHE``."""
         out = {}
+        spec = getattr(self.embedding, "cache_spec", lambda: None)()
+        if spec is not None:
+            out[self.EMBEDDING_CACHE] = spec
         for i, entry in enumerate(self.run):
             if entry.cache_of is None:
                 spec = self.blocks[entry.layer].mixer.cache_spec()
@@ -127,7 +133,8 @@ class Model:
     def forward(self, ctx, cache) -> torch.Tensor:
         """Float logits [len(ctx.logit_rows), vocab] of one step."""
         with span("embedding"):
-            residual = self.embedding.forward(ctx)
+            own = cache.view(self.EMBEDDING_CACHE, ctx.block_tables)
+            residual = self.embedding.forward(ctx) if own is None else self.embedding.forward(ctx, own)
         delta = None
         for i, entry in enumerate(self.run):
             owner = i if entry.cache_of is None else entry.cache_of

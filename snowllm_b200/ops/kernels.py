@@ -22,7 +22,9 @@ P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "elementwise": {
         "snk_embedding": [P, P, I, P, P, I, I, I, I, F, P],
-        "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P, P, P, I, P],
+        "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P, P, P, I, F, P, I, P],
+        "snk_pair_embedding": [P, P, I, P, P, P, I, I, I, I, F, LL, LL, LL, P, P, P, P, P, P],
+        "snk_softcap": [P, LL, F, P],
         "snk_residual_add": [P, P, LL, P],
         "snk_swiglu": [P, P, I, I, I, I, P],
     },
@@ -31,12 +33,14 @@ _SIGNATURES = {
     },
     "short_conv": {
         "snk_short_conv": [P, P, I, P, P, P, P, P, P, I, I, I, I, I, P],
+        "snk_causal_conv": [P, LL, P, I, P, P, P, P, P, P, LL, I, I, I, I, I, P],
     },
     "attention": {
         "snk_paged_attention_scratch_bytes": [I, I, I, I],
         "snk_paged_attention": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "snk_paged_attention_rows": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
         "snk_attention_merge": [P, P, P, I, I, I, I, I, I, I, P, P],
+        "snk_attention_merge_gated": [P, P, P, I, I, I, I, I, I, I, P, LL, I, P],
     },
     "attention_mma": {
         "snk_attention_prefill": [P, P, P, I, I, P, I, P, I, I, I, I, F, P],
@@ -100,7 +104,8 @@ _SIGNATURES = {
         "snk_split_prepare": [P, LL, I, I, I, P, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
         "snk_split_attention_tile_rows": [I, I, I, I, I, I, I],
         "snk_split_attention_decode_chunk": [I, I, I, I, I, I],
-        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, P, P, I, I, P, I, P],
+        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, P, P, I, P, LL, I, I, P,
+                                I, P],
     },
     "mlstm": {
         "snk_mlstm": [P, LL, I, I, I, I, I, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, P],
@@ -262,6 +267,41 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None =
     return out
 
 
+def pair_embedding(ids, table, pairs, buckets: int, mul_prev: int, mul_cur: int, row_seg, cu_seqlens, seg_start,
+                   seg_slot, last_token, pending=None, scale: float = 1.0, out=None):
+    """The embedding with a second table read by a hash of (previous token, token):
+    ``table[id] * scale + pairs[(prev * mul_prev + id * mul_cur) % buckets]``; a sequence's first token reads
+    ``pairs[buckets]``.  ``last_token`` int32 [slots]: the request's last token of earlier steps (read for a
+    segment that continues a sequence, then set to the segment's last token)."""
+    M = ids.numel()
+    V, H = table.shape
+    _chk(ids, "embedding ids", torch.int32)
+    if pending is not None:
+        _chk(pending, "pending tokens", torch.int32)
+    _chk(table, "embedding table", (torch.float32, torch.bfloat16))
+    _chk(pairs, "pair table", table.dtype, (buckets + 1, H))
+    _chk(last_token, "last tokens", torch.int32)
+    for name, t in (("row_seg", row_seg), ("cu_seqlens", cu_seqlens), ("seg_start", seg_start), ("seg_slot", seg_slot)):
+        _chk(t, name, torch.int32)
+    if out is None:
+        out = torch.empty(M, H, dtype=torch.float32, device=table.device)
+    _chk(out, "embedding output", torch.float32, (M, H))
+    check(fn("snk_pair_embedding")(_ptr(ids), _ptr(pending), pending.numel() if pending is not None else 0,
+                                   _ptr(table), _ptr(pairs), _ptr(out), M, H, V, code_of(table.dtype), float(scale),
+                                   int(buckets), int(mul_prev), int(mul_cur), _ptr(row_seg), _ptr(cu_seqlens),
+                                   _ptr(seg_start), _ptr(seg_slot), _ptr(last_token), _stream()), "pair_embedding",
+          work=lambda: (2 * M * H * table.element_size() + _nbytes(out, ids), 0))
+    return out
+
+
+def softcap(logits, cap: float):
+    """``logits <- cap * tanh(logits / cap)`` in place (float)."""
+    _chk(logits, "logits", torch.float32)
+    check(fn("snk_softcap")(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap",
+          work=lambda: (2 * _nbytes(logits), 0))
+    return logits
+
+
 class ExpertSum:
     """A residual delta that is still in pieces: the routed experts' outputs ``y`` [pairs, H] (float), where
     each (token, pick) pair's row lies (``pair_pos`` int32 [M*k]) and the picks' weights (``weights`` float
@@ -279,16 +319,31 @@ class ExpertSum:
 class DeltaSum:
     """A residual delta that is the sum of two sublayers' outputs (a layer whose mixer and feed-forward
     read the same normalised input): ``a`` a float tensor [M, H], ``b`` a float tensor or an ``ExpertSum``.
+    ``a_gate`` (float [M, n], its first column used): a logit per row whose sigmoid multiplies ``a``.
     A norm that knows it adds both into the residual itself; ``dense()`` forms the sum for anyone else."""
 
-    def __init__(self, a, b):
-        self.a, self.b = a, b
+    def __init__(self, a, b, a_gate=None):
+        self.a, self.b, self.a_gate = a, b, a_gate
         self.shape = tuple(a.shape)
 
     def dense(self) -> torch.Tensor:
-        out = self.a.clone()
+        out = self.a.clone() if self.a_gate is None else self.a * torch.sigmoid(self.a_gate[:, :1])
         residual_add(out, self.b.dense() if isinstance(self.b, ExpertSum) else self.b)
         return out
+
+
+class ScaledDelta:
+    """A residual delta that enters the stream times a constant: ``residual += scale * delta`` (``delta`` a
+    float tensor, an ``ExpertSum`` or a ``DeltaSum``).  The RMS norm's kernel applies the factor in its own
+    sum; ``dense()`` forms the product for anyone else."""
+
+    def __init__(self, delta, scale: float):
+        self.delta, self.scale = delta, float(scale)
+        self.shape = tuple(delta.shape)
+
+    def dense(self) -> torch.Tensor:
+        d = self.delta.dense() if hasattr(self.delta, "dense") else self.delta
+        return d * self.scale
 
 
 def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
@@ -296,12 +351,26 @@ def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
                 out: torch.Tensor | None = None) -> torch.Tensor:
     """``residual += delta`` (if given), then RMSNorm of the sum into the compute dtype.  With
     ``rows`` only those rows are normalised and the residual is left as it is.  ``delta`` is a float
-    tensor [M, H] or an ``ExpertSum``."""
+    tensor [M, H], an ``ExpertSum``, a ``DeltaSum`` of a tensor (with or without a gate per row) and an
+    ``ExpertSum``, or any of these in a ``ScaledDelta``."""
     M, H = residual.shape
     _chk(residual, "residual", torch.float32)
-    moe = None
+    moe = gate = None
+    dscale = 1.0
+    if isinstance(delta, ScaledDelta):
+        delta, dscale = delta.delta, delta.scale
     if isinstance(delta, DeltaSum):
-        delta = delta.dense()
+        if H % 4 == 0 and isinstance(delta.b, ExpertSum) and isinstance(delta.a, torch.Tensor):
+            moe, gate, delta = delta.b, delta.a_gate, delta.a
+            _chk(moe.y, "expert outputs", torch.float32)
+            _chk(moe.pair_pos, "pair positions", torch.int32, (M * moe.weights.shape[1],))
+            _chk(moe.weights, "top-k weights", torch.float32)
+            if gate is not None:
+                _chk(gate, "row gate", torch.float32)
+                if gate.dim() != 2 or gate.shape[0] != M:
+                    raise KernelError(f"row gate of shape {tuple(gate.shape)}, want [{M}, n]")
+        else:
+            delta = delta.dense()
     if isinstance(delta, ExpertSum):
         if H % 4 == 0:
             moe, delta = delta, None
@@ -323,7 +392,8 @@ def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
     check(fn("snk_add_rmsnorm")(_ptr(residual), _ptr(delta), _ptr(gamma), g32, _ptr(out), _ptr(rows),
                                 R, H, float(eps), code_of(dtype), _ptr(moe.y if moe else None),
                                 _ptr(moe.pair_pos if moe else None), _ptr(moe.weights if moe else None),
-                                moe.weights.shape[1] if moe else 0, _stream()), "add_rmsnorm",
+                                moe.weights.shape[1] if moe else 0, float(dscale), _ptr(gate),
+                                gate.shape[1] if gate is not None else 0, _stream()), "add_rmsnorm",
           work=lambda: (R * H * 4 + _nbytes(out, gamma) + (_nbytes(delta) + M * H * 4 if delta is not None else 0)
                         + ((moe.weights.shape[1] + 1) * M * H * 4 if moe else 0), 0))
     return out
@@ -685,6 +755,34 @@ def short_conv(bcx, weight, state, cu_seqlens, seg_start, seg_slot, row_seg, out
 
 # --- matrix products -------------------------------------------------------------------
 
+def causal_conv(u, channels: int, weight, state, cu_seqlens, seg_start, seg_slot, row_seg, out=None):
+    """Depthwise causal convolution over time on the first ``channels`` columns of ``u`` [M, width]:
+    y[t, c] = sum_j weight[c, j] * u~[t - taps + 1 + j, c], where u~ is the request's history (``state``
+    [slots, taps-1, channels], the last taps-1 rows of earlier steps; zeros for a fresh request) followed by
+    this step's rows; the state is brought up to date.  Returns y [M, channels]."""
+    M, width = u.shape
+    dtype = u.dtype
+    _chk(u, "conv input", (torch.float32, torch.bfloat16))
+    C, L = weight.shape
+    if C != channels or channels > width:
+        raise KernelError(f"conv weight {tuple(weight.shape)} over {channels} of {width} columns")
+    w32 = _small(weight, "conv weight", dtype)
+    _chk(state, "conv state", dtype)
+    if tuple(state.shape[1:]) != (max(L - 1, 0), C):
+        raise KernelError(f"conv state {tuple(state.shape)}, want [slots, {L - 1}, {C}]")
+    B = seg_start.numel()
+    if out is None:
+        out = torch.empty(M, C, dtype=dtype, device=u.device)
+    _chk(out, "conv output", dtype, (M, C))
+    fused = M == B and L > 1
+    check(fn("snk_causal_conv")(_ptr(u), width, _ptr(weight), w32, _ptr(state), _ptr(cu_seqlens), _ptr(seg_start),
+                                _ptr(seg_slot), _ptr(row_seg), _ptr(out), C, M, B, C, L, code_of(dtype), _stream()),
+          "causal_conv", launches=1 if fused or L == 1 else 2,
+          work=(lambda: (2 * M * C * u.element_size(), 2 * M * C * L)) if fused or L == 1 else
+          (lambda: [(2 * M * C * u.element_size(), 2 * M * C * L), (2 * B * (L - 1) * C * u.element_size(), 0)]))
+    return out
+
+
 def _gemm_work(rows, a, w, out, offsets):
     """(bytes, flops) of a product: a's rows and the result once, of a grouped W only the groups that own
     rows (a look at the offsets: only called with the ledger on)."""
@@ -884,13 +982,18 @@ def gather_rows(x, rows, div=1, out=None):
 # --- routed experts --------------------------------------------------------------------
 
 ROUTE_GEMM_MIN_ROWS = 64
+ROUTER_SCORINGS = ("sigmoid", "softmax", "softmax_picked")
 
 
 def _route_flags(norm_topk_prob, scoring: str) -> int:
     """The routing kernels' ``norm_topk`` argument: bit 0 renormalises the picks' weights by their sum, bit 1
-    scores with a softmax over all experts instead of a sigmoid per expert."""
-    if scoring not in ("sigmoid", "softmax"):
-        raise KernelError(f"router scoring {scoring!r} (known: sigmoid, softmax)")
+    scores with a softmax over all experts instead of a sigmoid per expert, bit 2 ("softmax_picked") picks by
+    the logits themselves (the bias then belongs to the logit) and weights by the softmax over the picked
+    logits alone."""
+    if scoring not in ROUTER_SCORINGS:
+        raise KernelError(f"router scoring {scoring!r} (known: {', '.join(ROUTER_SCORINGS)})")
+    if scoring == "softmax_picked":
+        return 4
     return int(bool(norm_topk_prob)) | (2 if scoring == "softmax" else 0)
 
 
@@ -1225,6 +1328,8 @@ def add_dyt(residual, delta, weight, bias, alpha, dtype, rows=None, out=None):
     M, H = residual.shape
     _chk(residual, "residual", torch.float32)
     da = db = moe = None
+    if isinstance(delta, ScaledDelta) or (isinstance(delta, DeltaSum) and delta.a_gate is not None):
+        delta = delta.dense()              # a factor or a gate per row: forms this kernel does not apply itself
     if isinstance(delta, DeltaSum):
         da, db = delta.a, delta.b
     elif delta is not None:
@@ -1405,14 +1510,15 @@ def heads_to_rows(x, out=None):
 
 def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, rot_dim, rot_mult, positions,
                   row_seg, block_table, page_size, kpool, vpool, nq, nkv, maps, dk, dv, write_kv=True,
-                  proj_bias=None, plain_norm=False):
+                  proj_bias=None, plain_norm=False, whole_norm=False):
     """Rows of a fused projection ``proj`` [M, width] (q at column ``q_off`` as [nq, dk], k at ``k_off`` as
     [nkv*maps, dk], v at ``v_off`` as [nkv, dv]): per-head RMS norm of q and k (if weights are given),
     rotation of the first ``rot_dim`` elements of each head by angle position * inv_freq with cos and sin
     times ``rot_mult`` (if ``inv_freq``), k and v written to their pools
     ([pages, nkv, page_size, maps*dk] and [pages, nkv, page_size, dv]); returns q [M, nq, dk].
     ``proj_bias`` (float [width]): added to the projection's columns first.  ``plain_norm``: q and k over
-    their root mean square without a weight."""
+    their root mean square without a weight.  ``whole_norm``: ONE root mean square over all heads of q (and
+    one over all of k), with weights of the projections' sizes [nq*dk] and [nkv*maps*dk]."""
     M, width = proj.shape
     dtype = proj.dtype
     _chk(proj, "projection", (torch.float32, torch.bfloat16))
@@ -1427,8 +1533,8 @@ def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, ro
         g32 = _small(q_gamma, "q norm weight", dtype)
         if _small(k_gamma, "k norm weight", dtype) != g32:
             raise KernelError("q and k norm weights must share a dtype")
-        _chk(q_gamma, "q norm weight", shape=(dk,))
-        _chk(k_gamma, "k norm weight", shape=(dk,))
+        _chk(q_gamma, "q norm weight", shape=(nq * dk if whole_norm else dk,))
+        _chk(k_gamma, "k norm weight", shape=(nkv * maps * dk if whole_norm else dk,))
     rot = int(rot_dim) if inv_freq is not None else 0
     if inv_freq is not None:
         _chk(inv_freq, "inv_freq", torch.float32, (rot // 2,))
@@ -1443,7 +1549,8 @@ def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, ro
                               f"{page_size}, {maps * dk}] and [pages, {nkv}, {page_size}, {dv}]")
     q_out = torch.empty(M, nq, dk, dtype=dtype, device=proj.device)
     check(fn("snk_split_prepare")(
-        _ptr(proj), width, q_off, k_off, v_off, _ptr(proj_bias), _ptr(q_gamma), _ptr(k_gamma), g32, int(has_norm),
+        _ptr(proj), width, q_off, k_off, v_off, _ptr(proj_bias), _ptr(q_gamma), _ptr(k_gamma), g32,
+        2 if whole_norm and has_norm else int(has_norm),
         float(eps),
         _ptr(inv_freq), rot, float(rot_mult), _ptr(positions), _ptr(row_seg), _ptr(block_table),
         block_table.shape[1], page_size, _ptr(kpool), _ptr(vpool), _ptr(q_out), M, nq, nkv * maps, nkv, dk, dv,
@@ -1479,7 +1586,8 @@ def reach_code(window=None, block=None) -> int:
 
 def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, *, maps=1, window=None,
                     bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None, num_chunks=1, scratch=None,
-                    chunk=SPLIT_ATTENTION_CHUNK, block=None, head_scale=None, sink=None):
+                    chunk=SPLIT_ATTENTION_CHUNK, block=None, head_scale=None, sink=None, keep=0, slopes=None,
+                    gate=None, gate_col=0):
     """Causal attention of q [M, nq, dk] (nq = heads * maps) over keys [pages, nkv, page_size, maps*dk] and
     values [pages, nkv, page_size, dv]; query head (h, map) reads the key at offset map*dk of its kv head.
     ``window``: the last ``window`` keys only; ``block``: the keys of the query's own block of ``block``
@@ -1489,8 +1597,11 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
     rows of one request, covering the step; None: every row alone.  ``num_chunks`` > 1 (rows alone only):
     a row's keys are cut into chunks of ``chunk`` (``split_attention_decode_chunk``) at absolute positions, one block each, and
     merged in chunk order (``num_chunks``: the most chunks a row spans; needs ``scratch`` bytes as
-    ``attention_scratch_bytes`` says).  Scores, weights and sums are float; returns [M, nq, dv] in
-    ``out_dtype`` (float32 or the compute dtype)."""
+    ``attention_scratch_bytes`` says).  ``keep``: beside its window a query also reaches the positions below
+    ``keep`` (``split_attention_chunks`` counts a row's chunks then).  ``slopes`` float [nq] (instead of
+    ``bias``): slopes[head] * (i - j) is taken off the scaled score.  ``gate`` [M, width] in the compute dtype:
+    head h's output is multiplied by sigmoid(gate[m, gate_col + h]).  Scores, weights and sums are float;
+    returns [M, nq, dv] in ``out_dtype`` (float32 or the compute dtype)."""
     M, nq, dk = q.shape
     dtype = q.dtype
     _chk(q, "q", (torch.float32, torch.bfloat16))
@@ -1507,9 +1618,20 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
         _chk(bias, "distance bias", torch.float32)
         if bias.dim() != 2 or bias.shape[0] != nq:
             raise KernelError(f"distance bias of shape {tuple(bias.shape)}, want [{nq}, distances]")
-    for name, t in (("head scale", head_scale), ("sink", sink)):
+    for name, t in (("head scale", head_scale), ("sink", sink), ("distance slopes", slopes)):
         if t is not None:
             _chk(t, name, torch.float32, (nq,))
+    if slopes is not None and bias is not None:
+        raise KernelError("a bias table and distance slopes exclude one another")
+    keep = int(keep or 0)
+    if keep and not window:
+        raise KernelError("kept first keys go with a sliding window")
+    gate_ptr, gate_ld = c_void_p(0), 0
+    if gate is not None:
+        _chk(gate, "head gate", dtype)
+        if gate.dim() != 2 or gate.shape[0] != M or gate_col + nq > gate.shape[1]:
+            raise KernelError(f"head gate of shape {tuple(gate.shape)} holds no {nq} columns from {gate_col} on")
+        gate_ptr, gate_ld = c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
     reach = reach_code(window, block)
     n_tiles = M
     if tiles is not None:
@@ -1520,6 +1642,8 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
     out_dtype = out_dtype or dtype
     if out_dtype not in (dtype, torch.float32):
         raise KernelError("attention output is the compute dtype or float32")
+    if gate is not None and out_dtype != dtype:
+        raise KernelError("gated heads come out in the compute dtype")
     if out is None:
         out = torch.empty(M, nq, dv, dtype=out_dtype, device=q.device)
     _chk(out, "attention output", out_dtype, (M, nq, dv))
@@ -1537,18 +1661,22 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
     def work():
         pos = positions.cpu().long()
         keys = (pos + 1).clamp(max=int(window)) if window else (pos % int(block) + 1 if block else pos + 1)
+        if keep:
+            keys = keys + (pos + 1 - int(window)).clamp(min=0, max=keep)
         total = int(keys.sum())
         return (-(-total // max(tile_rows, 1)) * nkv * (maps * dk + dv) * kpool.element_size() + _nbytes(q, out),
                 2 * nq * (dk + dv) * total)
     check(fn("snk_split_attention")(
         _ptr(q), _ptr(kpool), _ptr(vpool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
         _ptr(row_seg), _ptr(tiles), n_tiles, int(tile_rows), _ptr(out), int(out_dtype == torch.float32 and dtype != torch.float32),
-        nq, nkv, int(maps), dk, dv, reach, float(scale), _ptr(bias),
-        bias.shape[1] if bias is not None else 0, _ptr(head_scale), _ptr(sink), int(chunk), num_chunks, _ptr(scratch),
+        nq, nkv, int(maps), dk, dv, reach, float(scale), _ptr(bias if slopes is None else slopes),
+        -1 if slopes is not None else (bias.shape[1] if bias is not None else 0), _ptr(head_scale), _ptr(sink),
+        keep, gate_ptr, gate_ld, int(chunk), num_chunks, _ptr(scratch),
         code_of(dtype), _stream()), "split_attention", work=work)
     if num_chunks > 1:
-        check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, reach,
-                                        int(chunk), num_chunks, code_of(out_dtype), c_void_p(0), _stream()),
+        check(fn("snk_attention_merge_gated")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, reach, keep,
+                                              int(chunk), num_chunks, gate_ptr, gate_ld, code_of(out_dtype),
+                                              _stream()),
               "attention_merge", work=lambda: (M * nq * (dv + 2) * 4 * num_chunks + _nbytes(out), 0))
     return out
 
@@ -1702,6 +1830,8 @@ def streams_norm(streams, weight, groups, eps, dtype, *, init=None, update: Stre
         if update.streams is not streams:
             raise KernelError("the pending update belongs to other streams")
         y = update.y
+        if isinstance(y, ScaledDelta) or (isinstance(y, DeltaSum) and y.a_gate is not None):
+            y = y.dense()                  # a factor or a gate per row: forms this kernel does not apply itself
         if isinstance(y, DeltaSum):
             da, y = y.a, y.b
         if isinstance(y, ExpertSum):

@@ -1,7 +1,7 @@
 """Windowed grouped-query attention mixers whose keys and values have widths of their own
 (csrc/attention_split.cu): keys of ``head_dim``, values of ``v_head_dim``, kept in two pools.
 
-Three kinds are built on one class:
+Five kinds are built on one class:
 
 * ``bias_attention``: one softmax map per head; a learned bias is added to the scaled score, chosen by
   head and by a bucket of the distance i - j (``DistanceBuckets``).  No rotation.
@@ -16,6 +16,17 @@ Three kinds are built on one class:
   per head, one more term exp(sink) in the softmax's sum that has no key and no value; and a block-local
   mask: position i reads j <= i of its own block of ``block`` positions only (blocks counted from position
   0 of the sequence, whatever the cut into steps).
+
+* ``slope_attention``: one map per head, no rotation; q and k each over ONE root mean square taken over all
+  heads at once (weights of the projections' sizes); slope[h] * (i - j) is taken off the scaled score, with
+  slope[h] = 2^(-slope_range * (h + 1) / heads); a sliding window.
+* ``conv_gate_attention``: q, k and v pass a short causal convolution over time right after their projection
+  (depthwise, ``conv_taps`` taps; the last taps - 1 projected rows of a request are state of fixed size);
+  per-head RMS norm of q and k with one weight shared by all heads; rotary positions on the first
+  ``rot_dim`` elements; a sliding window beside the sequence's first ``keep_first`` positions, which stay
+  reachable at their true positions; one more term 1 in the softmax's denominator (``one_more``: a sink whose
+  score is 0 and which has no value); each head's output times sigmoid of the head's own logit from a gate
+  projection [heads, hidden] that reads the mixer's input.
 
 The first two: per-head RMS norm of q and k with one weight of ``head_dim`` shared by all heads (and maps), before
 the rotation; ``window`` keeps the last ``window`` keys.  Scores, softmax weights and the per-head
@@ -35,7 +46,7 @@ from ..ops import kernels, linear
 from . import attention_plan as plan
 from .base import Part
 from .registry import lookup, register_mixer
-from .spec import INIT_BIAS, INIT_ONES, KEEP_F32, KEEP_SMALL, PagedKVSpec, TensorSpec
+from .spec import INIT_BIAS, INIT_CONV, INIT_ONES, KEEP_F32, KEEP_SMALL, PagedKVSpec, SlotStateSpec, TensorSpec
 
 
 class DistanceBuckets:
@@ -98,16 +109,21 @@ class MapsAttention(Part):
     libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "attention_split", "attention", "sublayer")
     maps = 1
     norm_weights = True        # the per-head norm of q and k has a weight (False: the plain root mean square)
+    whole_norm = False         # True: ONE root mean square over all heads of q (of k), weights of that size
+    keep_first = 0             # positions at the sequence's start that stay reachable beside the window
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  v_head_dim: int, scale: float, qk_norm_eps: float | None, window: int | None = None,
                  cache_window: int | None = None, position: dict | None = None, reads_cache: bool = False,
-                 block: int | None = None):
+                 block: int | None = None, keep_first: int = 0):
         super().__init__(dtype, names)
+        if keep_first and (not window or keep_first < 0 or reads_cache or cache_window not in (None, window)):
+            raise ConfigError("kept first positions go with a sliding window on a cache of the layer's own")
+        self.keep_first = int(keep_first or 0)
         if block is not None and (window is not None or cache_window is not None or reads_cache or block < 1):
             raise ConfigError("a block-local mask stands alone: no window, no shared cache, a positive size")
         self.block = block
-        self.proj_bias = self.head_scale = self.sink = None      # float tensors a kind may bind
+        self.proj_bias = self.head_scale = self.sink = self.slopes = None      # float tensors a kind may bind
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
         if (num_heads // num_kv_heads) * self.maps > 32:
@@ -146,7 +162,7 @@ class MapsAttention(Part):
 
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.maps * self.head_dim, self.cache_window, self.v_head_dim,
-                           separate=True, block=self.block)
+                           separate=True, block=self.block, keep_first=self.keep_first)
 
     def declare(self, has):
         H, dk, dv, n = self.hidden_size, self.head_dim, self.v_head_dim, self.names
@@ -156,9 +172,10 @@ class MapsAttention(Part):
                       TensorSpec("v_proj", n["v_proj"], (self.num_kv_heads * dv, H))]
         specs.append(TensorSpec("out_proj", n["out_proj"], (H, self.num_heads * dv)))
         if self.qk_norm_eps is not None and self.norm_weights:
-            specs.append(TensorSpec("q_norm", n["q_norm"], (dk,), INIT_ONES, KEEP_SMALL))
+            nq, nk = (self.nq * dk, self.num_kv_heads * self.maps * dk) if self.whole_norm else (dk, dk)
+            specs.append(TensorSpec("q_norm", n["q_norm"], (nq,), INIT_ONES, KEEP_SMALL))
             if not self.reads_cache:
-                specs.append(TensorSpec("k_norm", n["k_norm"], (dk,), INIT_ONES, KEEP_SMALL))
+                specs.append(TensorSpec("k_norm", n["k_norm"], (nk,), INIT_ONES, KEEP_SMALL))
         return specs
 
     def _projection_rows(self, tensors) -> list:
@@ -182,15 +199,17 @@ class MapsAttention(Part):
             raise KernelError("a layer without key and value tensors must read another layer's cache, "
                               "and one with them must own its cache")
         proj = linear(x, self.w_in)
-        q_off, k_off, v_off, _, _ = self._columns()
+        q_off, k_off, v_off, g_off, _ = self._columns()
+        cache, rows = self._convolved(ctx, proj, cache)      # the rows that are normalised, turned and cached
         kpool, vpool = cache.pools
         inv_freq, rot_dim = self.position.rotary(x.device)
-        q = kernels.split_prepare(proj, q_off, k_off, v_off, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
+        q = kernels.split_prepare(rows, q_off, k_off, v_off, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
                                   inv_freq, rot_dim, getattr(self.position, "magnitude", 1.0), ctx.positions,
                                   ctx.row_seg, cache.block_table, cache.page_size, kpool, vpool, self.nq,
                                   self.num_kv_heads, self.maps, self.head_dim, self.v_head_dim,
                                   write_kv=owns_cache, proj_bias=self.proj_bias,
-                                  plain_norm=self.qk_norm_eps is not None and not self.norm_weights)
+                                  plain_norm=self.qk_norm_eps is not None and not self.norm_weights,
+                                  whole_norm=self.whole_norm)
         ctx.tap("attention_q", q)
         decode_only = max(ctx.host_seg_len) <= 1
         tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
@@ -199,18 +218,30 @@ class MapsAttention(Part):
         if decode_only:
             # rows of decoded tokens: their keys in chunks, one block each, merged in chunk order
             chunk = self._decode_chunk
-            num_chunks = plan.chunks(ctx, self.window, None, chunk, block=self.block)
+            num_chunks = plan.chunks(ctx, self.window, None, chunk, block=self.block, keep=self.keep_first)
             if self.window:                # a captured step plans for its longest sequence; a window spans fewer
-                num_chunks = min(num_chunks, (self.window - 1) // chunk + 2)
+                num_chunks = min(num_chunks, (self.window - 1) // chunk + 2 + -(-self.keep_first // chunk))
             if num_chunks > 1:
                 scratch = ctx.scratch(kernels.attention_scratch_bytes(ctx.M, self.nq, self.v_head_dim, num_chunks))
         out = kernels.split_attention(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
                                       ctx.row_seg, self.scale, maps=self.maps, window=self.window, bias=self.bias,
                                       tiles=attention_tiles(ctx, tile_rows), tile_rows=tile_rows,
                                       out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch, chunk=chunk,
-                                      block=self.block, head_scale=self.head_scale, sink=self.sink)
+                                      block=self.block, head_scale=self.head_scale, sink=self.sink,
+                                      keep=self.keep_first, slopes=self.slopes,
+                                      gate=proj if self._gate_in_kernel() else None, gate_col=g_off)
         ctx.tap("attention_o", out)
         return proj, out
+
+    def _convolved(self, ctx, proj, cache):
+        """(the paged view, the rows split_prepare reads): a kind whose projections pass something on their
+        way (a convolution with state of its own) does it here."""
+        return cache, proj
+
+    def _gate_in_kernel(self) -> bool:
+        """Whether the gate columns of the projection hold one logit per head that the attention kernel
+        applies itself."""
+        return False
 
 
 class BiasAttention(MapsAttention):
@@ -313,6 +344,94 @@ class SinkAttention(MapsAttention):
         return linear(out.view(ctx.M, -1), self.wo, out_dtype=torch.float32)
 
 
+class SlopeAttention(MapsAttention):
+    """One map per head, no rotation; q and k over one root mean square each, taken over all heads at once;
+    a distance penalty slope[h] * (i - j) with slope[h] = 2^(-slope_range * (h + 1) / heads)."""
+    whole_norm = True
+
+    def __init__(self, dtype, names, *, slope_range: float = 8.0, **kw):
+        super().__init__(dtype, names, **kw)
+        self.slope_range = float(slope_range)
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        H = self.num_heads
+        slopes = [2.0 ** (-self.slope_range * (h + 1) / H) for h in range(H)]
+        self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(self.w_in.device)
+
+    def forward(self, ctx, x, cache, owns_cache=True):
+        _, out = self._attend(ctx, x, cache, owns_cache, self.dtype)
+        return linear(out.view(ctx.M, -1), self.wo, out_dtype=torch.float32)
+
+
+class ConvGateAttention(MapsAttention):
+    """Convolved projections, kept first positions, one more term in the softmax's sum, gated heads."""
+
+    def __init__(self, dtype, names, *, conv_taps: int | None = None, one_more: bool = True, **kw):
+        super().__init__(dtype, names, **kw)
+        if self.reads_cache:
+            raise ConfigError("a layer with convolved projections owns its cache")
+        self.conv_taps = int(conv_taps) if conv_taps else 0
+        if self.conv_taps > 16:
+            raise ConfigError(f"conv taps {self.conv_taps}: the kernel takes up to 16")
+        self.one_more = bool(one_more)
+        self.conv_w = None
+
+    @property
+    def conv_channels(self) -> int:
+        return self.num_heads * self.head_dim + self.num_kv_heads * (self.head_dim + self.v_head_dim)
+
+    def _gate_width(self) -> int:
+        return self.num_heads
+
+    def _gate_in_kernel(self) -> bool:
+        return True
+
+    def cache_spec(self):
+        pages = super().cache_spec()
+        if self.conv_taps <= 1:
+            return pages
+        return (pages, SlotStateSpec(((self.conv_taps - 1, self.conv_channels),), ("compute",)))
+
+    def declare(self, has):
+        n, dk, dv = self.names, self.head_dim, self.v_head_dim
+        specs = super().declare(has) + [TensorSpec("gate_proj", n["gate_proj"], (self.num_heads, self.hidden_size))]
+        if self.conv_taps:
+            L = self.conv_taps
+            specs += [TensorSpec("q_conv", n["q_conv"], (self.num_heads * dk, L), INIT_CONV, KEEP_SMALL),
+                      TensorSpec("k_conv", n["k_conv"], (self.num_kv_heads * dk, L), INIT_CONV, KEEP_SMALL),
+                      TensorSpec("v_conv", n["v_conv"], (self.num_kv_heads * dv, L), INIT_CONV, KEEP_SMALL)]
+        return specs
+
+    def _projection_rows(self, tensors) -> list:
+        return super()._projection_rows(tensors) + [tensors["gate_proj"]]
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        if self.conv_taps:
+            self.conv_w = torch.cat([tensors[k] for k in ("q_conv", "k_conv", "v_conv")], 0).contiguous()
+        if self.one_more:          # a sink whose score is 0: exp(0) = 1 joins every row's sum
+            self.sink = torch.zeros(self.nq, dtype=torch.float32, device=self.w_in.device)
+
+    def _convolved(self, ctx, proj, cache):
+        if not self.conv_taps:
+            return cache, proj
+        if self.conv_taps == 1:            # one tap: a factor per channel, and no history to keep
+            pages, state = cache, proj.new_empty(1, 0, self.conv_channels)
+        else:
+            pages, state = cache[0], cache[1].tensors[0]
+        rows = kernels.causal_conv(proj, self.conv_channels, self.conv_w, state, ctx.cu_seqlens,
+                                   ctx.seg_start, ctx.seg_slot, ctx.row_seg)
+        ctx.tap("attention_conv", rows)
+        return pages, rows
+
+    def forward(self, ctx, x, cache, owns_cache=True):
+        _, out = self._attend(ctx, x, cache, owns_cache, self.dtype)
+        return linear(out.view(ctx.M, -1), self.wo, out_dtype=torch.float32)
+
+
 register_mixer("sink_attention", SinkAttention)
+register_mixer("slope_attention", SlopeAttention)
+register_mixer("conv_gate_attention", ConvGateAttention)
 register_mixer("bias_attention", BiasAttention)
 register_mixer("diff_attention", DiffAttention)

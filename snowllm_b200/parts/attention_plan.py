@@ -50,13 +50,15 @@ def _positions(ctx, rows):
     return ctx.host_positions if rows is None else ctx.host_positions[np.asarray(rows, dtype=np.int64)]
 
 
-def chunks(ctx, window=None, rows=None, chunk: int = ATTENTION_CHUNK, block=None) -> int:
+def chunks(ctx, window=None, rows=None, chunk: int = ATTENTION_CHUNK, block=None, keep: int = 0) -> int:
     """The most chunks of ``chunk`` keys that a row (of ``rows``, or of the step) spans; ``window``: a row
-    reaches its last ``window`` keys only; ``block``: the keys of its own block of ``block`` positions only.
+    reaches its last ``window`` keys only; ``block``: the keys of its own block of ``block`` positions only;
+    ``keep`` (with a window): the first ``keep`` positions that lie before a row's window come in chunks of
+    their own, counted from position 0, ahead of the window's.
     A captured step is planned for the longest sequence its launches may ever serve."""
     if ctx.capture_max_len is not None:
         n = max(1, -(-ctx.capture_max_len // chunk))
-        return min(n, (block - 1) // chunk + 2) if block else n
+        return min(n, (block - 1) // chunk + 2) if block else n + (-(-keep // chunk) if keep and window else 0)
     pos = _positions(ctx, rows)
     if len(pos) == 0:
         return 1
@@ -64,7 +66,8 @@ def chunks(ctx, window=None, rows=None, chunk: int = ATTENTION_CHUNK, block=None
         lo = pos - pos % block
     else:
         lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
-    return int((pos // chunk - lo // chunk).max()) + 1
+    kept = -(-np.minimum(keep, lo) // chunk) if keep and window else 0
+    return int((pos // chunk - lo // chunk + kept).max()) + 1
 
 
 def plan(ctx, window=None, rows=None) -> tuple[int, int]:

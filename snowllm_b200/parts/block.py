@@ -26,8 +26,12 @@ from .spec import KEEP_F32, TensorSpec
 
 
 class PreNormBlock:
-    def __init__(self, mixer, ffn, mixer_norm, ffn_norm):
+    """``residual_scale`` m (a constant of the arrangement): x += m * mixer(norm(x)); x += m * ffn(norm(x)).
+    The factor travels with the delta (``kernels.ScaledDelta``) to the norm that adds it."""
+
+    def __init__(self, mixer, ffn, mixer_norm, ffn_norm, *, dtype=None, residual_scale: float = 1.0):
         self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+        self.residual_scale = float(residual_scale)
         self._names = tuple(f"{what}:{type(part).__name__}" for what, part in
                             (("norm", mixer_norm), ("mixer", mixer), ("norm", ffn_norm), ("ffn", ffn)))
 
@@ -41,6 +45,8 @@ class PreNormBlock:
         with span(self._names[1]):
             delta = self.mixer.forward(ctx, x, cache, owns_cache)
         ctx.tap("mixer_out", delta)
+        if self.residual_scale != 1.0:
+            return self._scaled(ctx, residual, delta)
         if self.ffn is None:
             return delta
         fused = getattr(self.ffn, "forward_from_residual", None)
@@ -56,6 +62,20 @@ class PreNormBlock:
         with span(self._names[3]):
             delta = self.ffn.forward(ctx, x)
         ctx.tap("ffn_out", delta)
+        return delta
+
+    def _scaled(self, ctx, residual, delta):
+        """The rest of the layer when the sublayers' outputs enter the stream times a constant."""
+        delta = kernels.ScaledDelta(delta, self.residual_scale)
+        if self.ffn is not None:
+            with span(self._names[2]):
+                x = self.ffn_norm.forward(ctx, residual, delta)
+            ctx.tap("ffn_in", x)
+            with span(self._names[3]):
+                delta = kernels.ScaledDelta(self.ffn.forward(ctx, x), self.residual_scale)
+            ctx.tap("ffn_out", delta.delta)
+        if ctx.taps is not None:
+            ctx.tap("layer_out", residual + delta.dense())
         return delta
 
 

@@ -7,7 +7,8 @@ import torch
 from ..ops import kernels, linear
 from .base import Part
 from .registry import register_embedding, register_head
-from .spec import TensorSpec
+from ..errors import ConfigError
+from .spec import SlotStateSpec, TensorSpec
 
 
 class Embedding(Part):
@@ -33,13 +34,47 @@ class Embedding(Part):
         return kernels.embedding(ctx.token_ids, self.weight, pending=ctx.pending_tokens, scale=self.scale)
 
 
-class LinearHead(Part):
-    """logits = x . W^T in float.  ``tied``: W is the embedding table, and no tensor is declared."""
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2")
+class PairHashEmbedding(Embedding):
+    """The embedding plus a row of a second table chosen by a hash of the token and the one before it:
+    ``pairs[(previous * mul_prev + token * mul_cur) mod buckets]``; a sequence's first token reads the table's
+    extra last row (number ``buckets``).  The last token of a request's earlier steps is state of fixed size
+    (one int32 per slot), which the cache manager keeps like a mixer's."""
 
-    def __init__(self, dtype, names, *, vocab_size: int, hidden_size: int, tied: bool):
+    def __init__(self, dtype, names, *, vocab_size: int, hidden_size: int, buckets: int, mul_prev: int,
+                 mul_cur: int, scale: float = 1.0):
+        super().__init__(dtype, names, vocab_size=vocab_size, hidden_size=hidden_size, scale=scale)
+        if buckets < 1 or mul_prev < 0 or mul_cur < 0:
+            raise ConfigError(f"a pair table of {buckets} buckets with multipliers {mul_prev}, {mul_cur}")
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.pairs = None
+
+    def cache_spec(self):
+        return SlotStateSpec(((),), ("i32",))
+
+    def declare(self, has):
+        return super().declare(has) + [TensorSpec("pairs", self.names["pairs"], (self.buckets + 1, self.hidden_size))]
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.pairs = tensors["pairs"]
+
+    def forward(self, ctx, cache):
+        return kernels.pair_embedding(ctx.token_ids, self.weight, self.pairs, self.buckets, self.mul_prev,
+                                      self.mul_cur, ctx.row_seg, ctx.cu_seqlens, ctx.seg_start, ctx.seg_slot,
+                                      cache.tensors[0], pending=ctx.pending_tokens, scale=self.scale)
+
+
+class LinearHead(Part):
+    """logits = x . W^T in float.  ``tied``: W is the embedding table, and no tensor is declared.
+    ``softcap`` c: the logits are then c * tanh(logits / c)."""
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "elementwise")
+
+    def __init__(self, dtype, names, *, vocab_size: int, hidden_size: int, tied: bool, softcap: float | None = None):
         super().__init__(dtype, names)
         self.vocab_size, self.hidden_size, self.tied = vocab_size, hidden_size, tied
+        if softcap is not None and not softcap > 0:
+            raise ConfigError(f"a logit cap of {softcap}: want a positive number")
+        self.softcap = softcap
         self.weight = None
 
     def declare(self, has):
@@ -55,8 +90,10 @@ class LinearHead(Part):
         return self.weight.numel() * self.weight.element_size() if self.weight is not None else 0
 
     def forward(self, ctx, x):
-        return linear(x, self.weight, out_dtype=torch.float32)
+        logits = linear(x, self.weight, out_dtype=torch.float32)
+        return kernels.softcap(logits, self.softcap) if self.softcap else logits
 
 
 register_embedding("embedding", Embedding)
+register_embedding("pair_hash_embedding", PairHashEmbedding)
 register_head("linear_head", LinearHead)

@@ -39,18 +39,23 @@ class SwiGLU(Part):
 
 
 class GatedFFN(SwiGLU):
-    """down(act(gate x) * up x) with ``activation`` one of silu, relu, gelu_tanh: the bfloat16 products apply
-    the gate at their store (gate and up rows interleaved by 8); float32, and widths that are no multiple
-    of 8, run the product and then one elementwise kernel."""
+    """down(act(gate x) * up x) with ``activation`` one of silu, relu, gelu_tanh, or ``swish_clamp`` with its
+    ``limit`` (g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)): the
+    bfloat16 products apply the gate at their store (gate and up rows interleaved by 8); float32, and widths
+    that are no multiple of 8, run the product and then one elementwise kernel."""
+    libraries = SwiGLU.libraries + ("sublayer",)
 
-    def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+    def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 limit: float | None = None):
         super().__init__(dtype, names, hidden_size=hidden_size, intermediate_size=intermediate_size)
-        if activation not in kernels.ACTIVATIONS:
-            raise ConfigError(f"activation {activation!r} (known: {', '.join(kernels.ACTIVATIONS)})")
-        self.activation = activation
+        if activation not in kernels.GATED_ACTIVATIONS or activation == "relu2":
+            raise ConfigError(f"activation {activation!r} (known: silu, relu, gelu_tanh, swish_clamp)")
+        if activation == "swish_clamp" and not (limit and limit > 0):
+            raise ConfigError("the clamped activation needs a positive limit")
+        self.activation, self.limit = activation, float(limit or 0.0)
 
     def forward(self, ctx, x):
-        act = linear_glu(x, self.w13, self.interleaved, self.activation)
+        act = linear_glu(x, self.w13, self.interleaved, self.activation, self.limit)
         return linear(act, self.w2, out_dtype=torch.float32)
 
 

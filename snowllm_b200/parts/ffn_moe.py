@@ -10,7 +10,10 @@ Options for other designs: ``scoring`` "softmax" (scores are a softmax over ALL 
 largest are picked and used as they are unless ``norm_topk_prob``); ``activation`` "swish_clamp" with
 ``limit``: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1); ``shared``:
 one more expert of the same form (a width and a limit of its own) that every token passes, its output
-added (the sum is left as a ``kernels.DeltaSum``)."""
+added (the sum is left as a ``kernels.DeltaSum``); with ``shared["row_gate"]`` its output is first multiplied
+by sigmoid(w_sg . x), one number per token (tensor ``shared_row_gate`` [1, hidden]).  ``scoring``
+"softmax_picked": the router's logits, plus the bias ``expert_bias`` which is then a part of the logit, pick
+the k largest, and the weights are the softmax over the picked logits alone."""
 from __future__ import annotations
 
 import torch
@@ -32,8 +35,8 @@ class SigmoidMoE(Part):
         """``scale_input``: a pick's weight multiplies the expert's INPUT (the output is the plain sum of
         expert(w * x) over the picks) instead of its output.  ``shared``: {"intermediate_size", "limit"}."""
         super().__init__(dtype, names)
-        if scoring not in ("sigmoid", "softmax"):
-            raise ConfigError(f"router scoring {scoring!r} (known: sigmoid, softmax)")
+        if scoring not in kernels.ROUTER_SCORINGS:
+            raise ConfigError(f"router scoring {scoring!r} (known: {', '.join(kernels.ROUTER_SCORINGS)})")
         if activation not in ("silu", "swish_clamp"):
             raise ConfigError(f"expert activation {activation!r} (known: silu, swish_clamp)")
         if activation == "swish_clamp" and not (limit and limit > 0):
@@ -45,7 +48,7 @@ class SigmoidMoE(Part):
             raise ConfigError("an expert bias goes with sigmoid scores")
         self.scoring, self.activation, self.limit = scoring, activation, limit
         self.shared = dict(shared) if shared is not None else None
-        self.shared_w13 = self.shared_w2 = None
+        self.shared_w13 = self.shared_w2 = self.shared_row_gate = None
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.num_experts, self.top_k = num_experts, top_k
         self.norm_topk_prob, self.use_expert_bias = norm_topk_prob, use_expert_bias
@@ -75,6 +78,8 @@ class SigmoidMoE(Part):
             S = self.shared["intermediate_size"]
             specs += [TensorSpec("shared_gate", n["shared_gate"], (S, H)), TensorSpec("shared_up", n["shared_up"], (S, H)),
                       TensorSpec("shared_down", n["shared_down"], (H, S))]
+            if self.shared.get("row_gate"):
+                specs.append(TensorSpec("shared_row_gate", n["shared_row_gate"], (1, H)))
         return specs
 
     def bind(self, tensors):
@@ -96,6 +101,11 @@ class SigmoidMoE(Part):
             self.shared_w13 = (interleave_gate_up(tensors["shared_gate"], tensors["shared_up"]) if self.shared_interleaved
                                else torch.cat((tensors["shared_gate"], tensors["shared_up"]), 0).contiguous())
             self.shared_w2 = tensors["shared_down"]
+            if self.shared.get("row_gate"):
+                # the one gate row as a product of its own (rows padded to what the products take); its float
+                # output's first column is the logit
+                g = tensors["shared_row_gate"]
+                self.shared_row_gate = torch.cat((g, g.new_zeros(15, g.shape[1])), 0).contiguous()
 
     def bytes_read(self, bound, picked=None):
         """Router and bias whole; of the experts only those that were picked (``picked`` None: all)."""
@@ -135,7 +145,12 @@ class SigmoidMoE(Part):
         if self.shared is None:
             return routed
         act = linear_glu(x, self.shared_w13, self.shared_interleaved, self.activation, self.shared["limit"])
-        return kernels.DeltaSum(linear(act, self.shared_w2, out_dtype=torch.float32), routed)
+        gate = None
+        if self.shared_row_gate is not None:
+            gate = linear(x, self.shared_row_gate, out_dtype=torch.float32)
+            if ctx is not None:
+                ctx.tap("shared_row_gate", gate)
+        return kernels.DeltaSum(linear(act, self.shared_w2, out_dtype=torch.float32), routed, a_gate=gate)
 
     def _gate_up(self, x, offsets, rows_out, cap, a_rows, a_div):
         """The experts' activated gate|up product over the rows in expert order."""

@@ -12,8 +12,11 @@ from .registry import register_position
 
 
 class RotaryPosition:
-    def __init__(self, *, head_dim: int, theta: float, rot_dim: int | None = None):
-        self.head_dim, self.theta = head_dim, float(theta)
+    """``precise``: the table is worked out in double precision on the host and rounded to float once
+    (otherwise in float, as SnowLLM forms it)."""
+
+    def __init__(self, *, head_dim: int, theta: float, rot_dim: int | None = None, precise: bool = False):
+        self.head_dim, self.theta, self.precise = head_dim, float(theta), precise
         self.rot_dim = head_dim if rot_dim is None else rot_dim
         if self.rot_dim % 2 or self.rot_dim > head_dim:
             raise ValueError(f"rot_dim={self.rot_dim} must be even and at most head_dim={head_dim}")
@@ -21,7 +24,11 @@ class RotaryPosition:
 
     def rotary(self, device):
         if self._inv_freq is None or self._inv_freq.device != torch.device(device):
-            inv = 1.0 / (self.theta ** (torch.arange(0, self.rot_dim, 2, dtype=torch.float32) / self.rot_dim))
+            if self.precise:
+                inv = torch.tensor([self.theta ** (-2.0 * i / self.rot_dim) for i in range(self.rot_dim // 2)],
+                                   dtype=torch.float64).to(torch.float32)
+            else:
+                inv = 1.0 / (self.theta ** (torch.arange(0, self.rot_dim, 2, dtype=torch.float32) / self.rot_dim))
             self._inv_freq = inv.to(device)
         return self._inv_freq, self.rot_dim
 

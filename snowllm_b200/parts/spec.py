@@ -83,11 +83,18 @@ class ModelSpec:
 
 # --- what a mixer asks of the cache manager -------------------------------------------
 
-def first_reachable(reach: int | None, pos: int) -> int:
-    """The first position that a query at ``pos`` (or later) can still read under ``reach``
-    (``PagedKVSpec.reach``)."""
+def kept_positions(reach) -> int:
+    """How many of a sequence's first positions stay reachable whatever the window (``PagedKVSpec.reach``)."""
+    return reach[1] if isinstance(reach, tuple) else 0
+
+
+def first_reachable(reach, pos: int) -> int:
+    """The first position of the sliding part that a query at ``pos`` (or later) can still read under
+    ``reach`` (``PagedKVSpec.reach``); positions below ``kept_positions(reach)`` stay reachable beside it."""
     if reach is None:
         return 0
+    if isinstance(reach, tuple):
+        reach = reach[0]
     if reach > 0:
         return max(0, pos - reach + 1)
     return pos - pos % (-reach)
@@ -106,7 +113,9 @@ class PagedKVSpec:
     ``v_head_dim`` 0 there is the key tensor alone (a latent row per position, a cache of keys only).
     ``separate`` asks for the two tensors also where the widths happen to be equal (a kernel that reads
     keys and values from pools of their own).
-    ``cache_dtype`` None keeps the rows in the compute dtype; "float32" or "bfloat16" fixes it."""
+    ``cache_dtype`` None keeps the rows in the compute dtype; "float32" or "bfloat16" fixes it.
+    ``keep_first`` (with a window): the sequence's first ``keep_first`` positions stay reachable beside the
+    window, so their pages are never given back."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
@@ -114,12 +123,18 @@ class PagedKVSpec:
     cache_dtype: str | None = None
     separate: bool = False
     block: int | None = None
+    keep_first: int = 0
 
     @property
-    def reach(self) -> int | None:
-        """What the cache manager groups layers by: None every row, W > 0 a window of W, -C a block of C."""
+    def reach(self):
+        """What the cache manager groups layers by: None every row, W > 0 a window of W, -C a block of C,
+        (W, K) a window of W beside the first K positions."""
         if self.window and self.block:
             raise ValueError("a cache keeps a window or a block, not both")
+        if self.keep_first and not self.window:
+            raise ValueError("kept first positions go with a window")
+        if self.window and self.keep_first:
+            return (self.window, self.keep_first)
         return self.window if self.window else (-self.block if self.block else None)
 
     @property
@@ -147,6 +162,6 @@ class PagedKVSpec:
 @dataclass(frozen=True)
 class SlotStateSpec:
     """State of fixed size per request: one tensor per shape, indexed by the request's slot.
-    ``dtypes`` entries are "compute" or "f32"."""
+    ``dtypes`` entries are "compute", "f32" or "i32"."""
     shapes: tuple[tuple[int, ...], ...]
     dtypes: tuple[str, ...] = ()
