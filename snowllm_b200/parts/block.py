@@ -48,6 +48,7 @@ class PreNormBlock:
         if self.residual_scale != 1.0:
             return self._scaled(ctx, residual, delta)
         if self.ffn is None:
+            self._tap_layer(ctx, residual, delta)
             return delta
         fused = getattr(self.ffn, "forward_from_residual", None)
         if fused is not None:          # a feed-forward that can take the norm before it into its first kernel
@@ -55,6 +56,7 @@ class PreNormBlock:
                 out = fused(ctx, residual, delta, self.ffn_norm)
             if out is not None:
                 ctx.tap("ffn_out", out)
+                self._tap_layer(ctx, residual, out)
                 return out
         with span(self._names[2]):
             x = self.ffn_norm.forward(ctx, residual, delta)
@@ -62,7 +64,13 @@ class PreNormBlock:
         with span(self._names[3]):
             delta = self.ffn.forward(ctx, x)
         ctx.tap("ffn_out", delta)
+        self._tap_layer(ctx, residual, delta)
         return delta
+
+    @staticmethod
+    def _tap_layer(ctx, residual, delta):
+        if ctx.taps is not None:
+            ctx.tap("layer_out", residual + (delta.dense() if hasattr(delta, "dense") else delta))
 
     def _scaled(self, ctx, residual, delta):
         """The rest of the layer when the sublayers' outputs enter the stream times a constant."""
@@ -74,8 +82,7 @@ class PreNormBlock:
             with span(self._names[3]):
                 delta = kernels.ScaledDelta(self.ffn.forward(ctx, x), self.residual_scale)
             ctx.tap("ffn_out", delta.delta)
-        if ctx.taps is not None:
-            ctx.tap("layer_out", residual + delta.dense())
+        self._tap_layer(ctx, residual, delta)
         return delta
 
 

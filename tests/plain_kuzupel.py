@@ -64,9 +64,12 @@ def rotate_halves(x, positions, base: float, dims: int):
     return out
 
 
-def window_mask(T: int, size: int, keep_first: int = 0):
-    """[T, T] bool: i sees j <= i with i - j < size, or j among the first ``keep_first`` positions."""
+def window_mask(T: int, size, keep_first: int = 0):
+    """[T, T] bool: i sees j <= i with i - j < size (None: every j <= i), or j among the first ``keep_first``
+    positions."""
     i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    if size is None:
+        return j <= i
     return (j <= i) & ((i - j < size) | (j < keep_first))
 
 
@@ -91,7 +94,7 @@ def slope_attention(h, t, m: dict, eps: float, p: str):
     q = (rms(h @ t[p + "q"].T, eps) * t[p + "q.norm"]).view(T, H, d)
     k = (rms(h @ t[p + "k"].T, eps) * t[p + "k.norm"]).view(T, G, d)
     v = (h @ t[p + "v"].T).view(T, G, dv)
-    mask = window_mask(T, m["mask"]["size"])
+    mask = window_mask(T, (m.get("mask") or {}).get("size"))
     dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).to(h.dtype)
     out = []
     for head in range(H):
@@ -118,7 +121,7 @@ def conv_gated_attention(h, t, m: dict, eps: float, p: str, positions):
     if rot is not None:
         q = rotate_halves(q, positions, rot["base"], rot["dims"])
         k = rotate_halves(k, positions, rot["base"], rot["dims"])
-    mask = window_mask(T, m["mask"]["size"], m["mask"].get("keep_first", 0))
+    mask = window_mask(T, (m.get("mask") or {}).get("size"), (m.get("mask") or {}).get("keep_first", 0))
     gate = torch.sigmoid(h @ t[p + "g"].T)                       # [T, H]
     out = []
     for head in range(H):
