@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine at the layer sizes of the LFM2.5 models, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--config 8b-a1b|dense-1.2b|dense-2.6b]
-    python bench.py --design beledra|zafopel|toderax   (another design beside the closest existing model at equal size; one JSON line)
+    python bench.py --design beledra|zafopel|toderax|kuzupel   (another design beside the closest existing model at equal size; one JSON line)
                     [--batch B] [--context C] [--dtype bfloat16|float32] [--impl ours|reference]
 
 Prints ONE JSON line.  Without flags: LFM2.5-8B-A1B sizes, 8 requests at context 8,192.
@@ -195,6 +195,36 @@ def _lfm2_moe_hybrid_like(width: int, layers: int, ff: int, vocab: int = 65536) 
             "use_expert_bias": True, "routed_scaling_factor": 1.0}
 
 
+def _kuzupel(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """Kuzupel at sizes that resemble a real model's layers: heads of 64, one kv head per four heads; layers
+    in turns with convolved projections (4 taps), half of each head turning, a window of 1,024 beside the first
+    64 positions, one more term in the softmax's sum and gated heads, and with a window of 2,048, norms over
+    the whole projection and a distance slope per head; the first layer's feed-forward dense, the others 4 of
+    32 experts of ff/8 and a shared expert of ff/8 behind its gate; a pair table of 65,521 buckets; sublayers
+    enter the stream times 0.5; logits capped at 30."""
+    heads = width // 64
+    common = {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 64, "vdim": 64, "scale": 0.125}
+    first = dict(common, conv=4, mask={"size": 1024, "keep_first": 64}, rot={"dims": 32, "base": 10000.0})
+    second = dict(common, mask={"size": 2048})
+    moe = {"kind": "moe", "expert": {"ff": ff // 8, "limit": 7.0}, "router": {"experts": 32, "top": 4},
+           "shared": {"ff": ff // 8, "limit": 7.0}}
+    out = [{"type": "attention" if i % 2 else "attention_2", "mixer": second if i % 2 else first,
+            "mlp": moe if i else {"kind": "dense", "ff": ff, "limit": 7.0}} for i in range(layers)]
+    return {"architecture": "Kuzupel", "vocab": vocab, "width": width, "residual_mult": 0.5, "logit_softcap": 30.0,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 17}},
+            "norm": {"eps": 1e-5}, "layers": json.loads(json.dumps(out))}
+
+
+def _lfm2_moe_heads64_like(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """The closest existing model at equal size: LFM2 with routed experts, attention in every layer with heads
+    of 64 and one kv head per four, the same width and depth, one dense layer first, then 4 of 32 experts of
+    ff/8."""
+    cfg = _lfm2_moe_like(width, layers, ff, vocab)
+    heads = width // 64
+    cfg.update(num_attention_heads=heads, num_key_value_heads=max(heads // 4, 1))
+    return cfg
+
+
 DESIGN_SIZES = {"w2048-l12": (2048, 12, 8192), "w1024-l6": (1024, 6, 4096)}
 # design -> (its name, its configuration at a size, the closest existing model at that size, what that is)
 DESIGNS = {"beledra": ("Beledra", _beledra, ("lfm2_dense", _lfm2_like),
@@ -203,7 +233,10 @@ DESIGNS = {"beledra": ("Beledra", _beledra, ("lfm2_dense", _lfm2_like),
                        "LFM2 with routed experts at equal width, depth, head count and size, expert count and width"),
            "toderax": ("Toderax", _toderax, ("lfm2_moe_hybrid", _lfm2_moe_hybrid_like),
                        "LFM2 with routed experts at equal width and depth: a short convolution where the design has a "
-                       "memory alone, attention with equal head counts where it has a pair, equal expert count and width")}
+                       "memory alone, attention with equal head counts where it has a pair, equal expert count and width"),
+           "kuzupel": ("Kuzupel", _kuzupel, ("lfm2_moe_heads64", _lfm2_moe_heads64_like),
+                       "LFM2 with routed experts at equal width, depth, head count and size (64), expert count and width; "
+                       "its attention sees every key, the design's a window")}
 
 
 def design_compare(a) -> dict:

@@ -39,6 +39,14 @@
 // values nothing more.  P in tensor memory as well, in the scores' place (256 columns hold no second place),
 // gave 600 us: the next tile's Q K^T must then wait for P V.
 // Every wait is bounded by wall time; a block that gives up sets a status word (snk_attention_tc_status).
+//
+// Options for mixers that bring more than a causal or windowed softmax (null or 0: off):
+//   keys and values in pools of their own [pages, kv heads, page_size, 64] (a second tensor map);
+//   `keep`: beside its window a row sees the positions below `keep`; the tiles of kept keys that lie before the
+//   window's first tile are walked first, in ascending order;
+//   `slopes`: slope[head] * (p - kp) is taken off the scaled score;
+//   `sink`: one more term exp(sink[head]) in the row's sum, without a key or a value (the row starts from it);
+//   `gate`: the head's output times sigmoid(gate[row * gate_ld + head]).
 #include "tcgen05.cuh"
 
 #define AT_BQ 128
@@ -142,11 +150,20 @@ __device__ __forceinline__ float at_exp2(float x) {
   return y;
 }
 
+// EXTRA false: the kernel without the options (they cost registers that the plain walk has no room for).
+template <bool EXTRA>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            const __grid_constant__ CUtensorMap map_v, int k_mul, int v_add,
                             const int* __restrict__ block_table, int max_pages, int page_size,
                             const int* __restrict__ tiles, int n_tiles, bf16* __restrict__ out, int nh, int nkv,
-                            int window, float scale_log2) {
+                            int window, float scale_log2, int keep, const float* __restrict__ slopes,
+                            const float* __restrict__ sink, const bf16* __restrict__ gate, long long gate_ld) {
+  if (!EXTRA) {
+    keep = 0;
+    slopes = sink = nullptr;
+    gate = nullptr;
+  }
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* sm_k = smem;                                             // [AT_KSTAGES][128 keys][64], swizzled by TMA
   unsigned char* sm_v = sm_k + (size_t)AT_KSTAGES * AT_KV_BYTES;          // [AT_VSTAGES][128 keys][64]
@@ -158,6 +175,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
     mbar_init(&sh->q_full, 1);
     mbar_init(&sh->q_ready, 4);
     for (int i = 0; i < AT_KSTAGES; ++i) {
@@ -195,7 +213,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int last_pos = pos0 + rows - 1;
   const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;          // the lowest key any row sees
   const int k_first = (key_lo / AT_BK) * AT_BK;
-  const int n_kt = (last_pos - k_first) / AT_BK + 1;
+  // tiles of kept first keys that lie wholly before the window's first tile: walked first
+  const int n_keep = keep > 0 ? min((keep + AT_BK - 1) / AT_BK, k_first / AT_BK) : 0;
+  const int n_kt = n_keep + (last_pos - k_first) / AT_BK + 1;
+  auto tile_k0 = [&](int j) { return j < n_keep ? j * AT_BK : k_first + (j - n_keep) * AT_BK; };
 
   if (warp == 0) {
     const int* bt = block_table + (size_t)seg * max_pages;
@@ -207,9 +228,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // completed, long before the tile's values are.  A tile has at most 16 pages: lane i looks up page i,
     // one tile ahead, so that the look-up (a trip to L2) is not part of the wait for a free slot.
     auto tile_pages = [&](int j, int& first_page, int& n_pages) {
-      const int k0 = k_first + j * AT_BK;
-      first_page = max(k0, key_lo) / page_size;
-      n_pages = min(k0 + AT_BK - 1, last_pos) / page_size - first_page + 1;
+      const int k0 = tile_k0(j);
+      // a tile that holds kept keys is loaded from its start; a tile of kept keys alone up to the last of them
+      first_page = (k0 < keep ? k0 : max(k0, key_lo)) / page_size;
+      const int last_key = j < n_keep ? min(k0 + AT_BK - 1, keep - 1) : min(k0 + AT_BK - 1, last_pos);
+      n_pages = last_key / page_size - first_page + 1;
     };
     // The keys run one tile ahead of the values (K[0], K[1], V[0], K[2], V[1], ...): a slot of values is
     // free late, and keys asked for behind that wait would be late too.
@@ -224,7 +247,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       if (t < n_kt) {
         const int ks = t % AT_KSTAGES;
-        const int k0 = k_first + t * AT_BK;
+        const int k0 = tile_k0(t);
         tile_pages(t, fp_k, np_k);
         at_wait(&sh->k_empty[ks], ((t / AT_KSTAGES) & 1) ^ 1, aborted, AT_ERR_KV_FREE);
         if (__any_sync(0xffffffffu, *aborted)) break;      // a wait ran out: nothing more is issued
@@ -232,18 +255,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         __syncwarp();
         if (lane < np_k)
           tma_load_2d(sm_k + (size_t)ks * AT_KV_BYTES + ((fp_k + lane) * page_size - k0) * 128, &map_kv,
-                      &sh->k_full[ks], 0, ((page_k * 2) * nkv + kvh) * page_size);
+                      &sh->k_full[ks], 0, ((page_k * k_mul) * nkv + kvh) * page_size);
       }
       if (t >= 1) {
         const int j = t - 1, vs = j % AT_VSTAGES;
-        const int k0 = k_first + j * AT_BK;
+        const int k0 = tile_k0(j);
         at_wait(&sh->v_empty[vs], ((j / AT_VSTAGES) & 1) ^ 1, aborted, AT_ERR_KV_FREE);
         if (__any_sync(0xffffffffu, *aborted)) break;
         if (lane == 0) mbar_expect_tx(&sh->v_full[vs], (uint32_t)np_v * page_size * 128u);
         __syncwarp();
         if (lane < np_v)
-          tma_load_2d(sm_v + (size_t)vs * AT_KV_BYTES + ((fp_v + lane) * page_size - k0) * 128, &map_kv,
-                      &sh->v_full[vs], 0, ((page_v * 2 + 1) * nkv + kvh) * page_size);
+          tma_load_2d(sm_v + (size_t)vs * AT_KV_BYTES + ((fp_v + lane) * page_size - k0) * 128, &map_v,
+                      &sh->v_full[vs], 0, ((page_v * k_mul + v_add) * nkv + kvh) * page_size);
       }
       fp_v = fp_k; np_v = np_k; page_v = page_k;                          // this round's keys are the next round's values
       page_k = page_next;
@@ -307,9 +330,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (lane == 0) mbar_arrive(&sh->q_ready);
     }
     float m_ref = -INFINITY, l = 0.f;                    // the maximum the exponentials are taken against (scaled), the sum
+    if (sink) {                                          // a term without a key: the row starts from it
+      const float sk = sink[head] * 1.4426950408889634f;
+      m_ref = ceilf(sk);
+      l = at_exp2(sk - m_ref);
+    }
+    const float slope_q = slopes ? slopes[head] * 1.4426950408889634f / scale_log2 : 0.f;   // in units of q . k
     for (int j = 0; j < n_kt; ++j) {
       const int st = j % AT_VSTAGES;
-      const int k0 = k_first + j * AT_BK;
+      const int k0 = tile_k0(j);
       at_wait(&sh->s_full, j & 1, aborted, AT_ERR_S);
       if (__any_sync(0xffffffffu, *aborted)) break;        // the whole warp leaves together
       tc_fence_after();
@@ -320,6 +349,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->s_empty);
+      if (slopes) {                                      // the distance penalty, before the scale: s - (slope / scale) (p - kp)
+        const float base = slope_q * (float)(k0 - pos);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[c][i] = __float_as_uint(fmaf(slope_q, (float)(c * 32 + i), __uint_as_float(r[c][i])) + base);
+      }
       // tiles that cross an edge: a key above the first row's position, or below the last row's window
       if (k0 + AT_BK - 1 > pos0 || k0 < lo_last) {
 #pragma unroll
@@ -327,7 +364,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int kp = k0 + c * 32 + i;
-            if (kp > pos || kp < lo) r[c][i] = 0xff800000u;      // -inf
+            if (kp > pos || (kp < lo && kp >= keep)) r[c][i] = 0xff800000u;      // -inf
           }
       }
       float mc[4];                                       // chains side by side (a maximum does not depend on the order)
@@ -388,7 +425,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (k0 < key_lo || k0 + AT_BK - 1 > last_pos) {    // value rows no row sees: zero, whatever they held
         at_wait(&sh->v_full[st], (j / AT_VSTAGES) & 1, aborted, AT_ERR_KV);
         const int kp = k0 + row;
-        if (kp < key_lo || kp > last_pos) {
+        if ((kp < key_lo && kp >= keep) || kp > last_pos) {
           uint4* v_row = reinterpret_cast<uint4*>(sm_v + (size_t)st * AT_KV_BYTES + row * 128);
 #pragma unroll
           for (int i = 0; i < 8; ++i) v_row[i] = make_uint4(0, 0, 0, 0);
@@ -411,7 +448,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     at_wait(&sh->pv_done, (n_kt - 1) & 1, aborted, AT_ERR_PV);
     tc_fence_after();
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (gate && row < rows) inv /= 1.f + expf(-__bfloat162float(gate[(size_t)(row0 + row) * gate_ld + head]));
     bf16* dst = out + ((size_t)(row0 + row) * nh + head) * AT_HD;
 #pragma unroll
     for (int c = 0; c < AT_HD / 32; ++c) {
@@ -445,31 +483,69 @@ static bool at_page_ok(int page_size) {
 // q [M, nh, 64], out [M, nh * 64] bfloat16; tiles int32 [n, 4] = (segment, first row, rows <= 128, position of
 // the first row); num_pages: pages in the pool [pages, 2, nkv, page_size, 64].  Sizes it does not take give
 // SNK_ERR_SIZE (the caller then uses the mma.sync kernels).
-SNK_API int snk_attention_prefill_tc(const void* q, long long M, const void* pool, long long num_pages,
-                                     const int* block_table, int max_pages, int page_size, const int* tiles,
-                                     int n_tiles, void* out, int nh, int nkv, int hd, int window, float scale,
-                                     cudaStream_t stream) {
+static int at_launch(const void* q, long long M, const void* pool, const void* vpool, long long num_pages,
+                     const int* block_table, int max_pages, int page_size, const int* tiles, int n_tiles, void* out,
+                     int nh, int nkv, int hd, int window, float scale, int keep, const float* slopes,
+                     const float* sink, const void* gate, long long gate_ld, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (nkv <= 0 || nh % nkv || nh > 65535 || M <= 0) return SNK_ERR_SIZE;
   if (hd != AT_HD || !at_page_ok(page_size) || num_pages <= 0) return SNK_ERR_SIZE;
   if (num_pages * 2 * nkv * page_size >= (1ll << 31)) return SNK_ERR_SIZE;
-  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16) || ((uintptr_t)out % 16)) return SNK_ERR_ALIGN;
-  CUtensorMap map_q, map_kv;
+  if (keep < 0 || (keep > 0 && window <= 0) || !(scale > 0.f)) return SNK_ERR_SIZE;
+  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16) || ((uintptr_t)vpool % 16) || ((uintptr_t)out % 16))
+    return SNK_ERR_ALIGN;
+  // vpool null: keys and values of a page side by side in one pool [pages, 2, kv heads, page_size, 64]
+  const int k_mul = vpool ? 1 : 2, v_add = vpool ? 0 : 1;
+  CUtensorMap map_q, map_kv, map_v;
   int rc = tensor_map(q, M, (long long)nh * hd, AT_BQ, 64, &map_q);
   if (rc) return rc;
-  rc = tensor_map(pool, num_pages * 2 * nkv * page_size, hd, page_size, 64, &map_kv);
+  rc = tensor_map(pool, num_pages * k_mul * nkv * page_size, hd, page_size, 64, &map_kv);
   if (rc) return rc;
+  map_v = map_kv;
+  if (vpool) {
+    rc = tensor_map(vpool, num_pages * nkv * page_size, hd, page_size, 64, &map_v);
+    if (rc) return rc;
+  }
   const size_t smem = (size_t)(AT_KSTAGES + AT_VSTAGES) * AT_KV_BYTES + AT_P_BYTES + sizeof(AtShared);
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     configured = true;
   }
-  snk_launch(attention_prefill_tc_kernel, dim3(n_tiles, nh), dim3(AT_THREADS), smem, stream, map_q, map_kv,
-             block_table, max_pages, page_size, tiles, n_tiles, static_cast<bf16*>(out), nh, nkv, window,
-             scale * 1.4426950408889634f);
+  if (keep || slopes || sink || gate)
+    snk_launch(attention_prefill_tc_kernel<true>, dim3(n_tiles, nh), dim3(AT_THREADS), smem, stream, map_q, map_kv,
+               map_v, k_mul, v_add, block_table, max_pages, page_size, tiles, n_tiles, static_cast<bf16*>(out), nh,
+               nkv, window, scale * 1.4426950408889634f, keep, slopes, sink, static_cast<const bf16*>(gate), gate_ld);
+  else
+    snk_launch(attention_prefill_tc_kernel<false>, dim3(n_tiles, nh), dim3(AT_THREADS), smem, stream, map_q, map_kv,
+               map_v, k_mul, v_add, block_table, max_pages, page_size, tiles, n_tiles, static_cast<bf16*>(out), nh,
+               nkv, window, scale * 1.4426950408889634f, 0, static_cast<const float*>(nullptr),
+               static_cast<const float*>(nullptr), static_cast<const bf16*>(nullptr), 0LL);
   SNK_LAUNCH_CHECK();
   return 0;
+}
+
+SNK_API int snk_attention_prefill_tc(const void* q, long long M, const void* pool, long long num_pages,
+                                     const int* block_table, int max_pages, int page_size, const int* tiles,
+                                     int n_tiles, void* out, int nh, int nkv, int hd, int window, float scale,
+                                     cudaStream_t stream) {
+  return at_launch(q, M, pool, nullptr, num_pages, block_table, max_pages, page_size, tiles, n_tiles, out, nh, nkv,
+                   hd, window, scale, 0, nullptr, nullptr, nullptr, 0, stream);
+}
+
+// The same with keys [pages, nkv, page_size, 64] and values [pages, nkv, page_size, 64] in pools of their own,
+// kept first keys, a distance slope and a sink per head (float [nh]) and a gate per (row, head) (bfloat16,
+// gate[row * gate_ld + head]); each of them may be off (0 or null).
+SNK_API int snk_attention_prefill_tc_split(const void* q, long long M, const void* kpool, const void* vpool,
+                                           long long num_pages, const int* block_table, int max_pages,
+                                           int page_size, const int* tiles, int n_tiles, void* out, int nh, int nkv,
+                                           int hd, int window, float scale, int keep, const float* slopes,
+                                           const float* sink, const void* gate, long long gate_ld,
+                                           cudaStream_t stream) {
+  if (!vpool) return SNK_ERR_SIZE;
+  return at_launch(q, M, kpool, vpool, num_pages, block_table, max_pages, page_size, tiles, n_tiles, out, nh, nkv,
+                   hd, window, scale, keep, slopes, sink, gate, gate_ld, stream);
 }
 
 // Queue a copy of the status word into ``host`` (pinned host memory, one int) on ``stream`` without waiting

@@ -52,6 +52,7 @@ _SIGNATURES = {
     },
     "attention_tc": {
         "snk_attention_prefill_tc": [P, LL, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
+        "snk_attention_prefill_tc_split": [P, LL, P, P, LL, P, I, I, P, I, P, I, I, I, I, F, I, P, P, P, LL, P],
         "snk_attention_tc_status": [],
         "snk_attention_tc_status_peek": [P, P],
     },
@@ -605,6 +606,51 @@ def attention_prefill_tc(q, pool, block_table, page_size, tiles, scale, out, win
         _ptr(q), M, _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles),
         tiles.shape[0], _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()),
         "attention_prefill_tc", work=lambda: _tiles_attention_work(q, pool, tiles, window))
+    return out
+
+
+def attention_prefill_tc_split(q, kpool, vpool, block_table, page_size, tiles, scale, out, *, window=None, keep=0,
+                               slopes=None, sink=None, gate=None, gate_col=0):
+    """``attention_prefill_tc`` over keys and values in pools of their own [pages, kv heads, page_size, 64], with
+    the options of ``split_attention``: ``keep`` first positions beside the window, ``slopes`` and ``sink`` float
+    [heads], ``gate`` [M, width] bfloat16 whose columns from ``gate_col`` hold a logit per head."""
+    M, nh, hd = q.shape
+    _chk(q, "q", torch.bfloat16)
+    _chk(kpool, "key pool", torch.bfloat16)
+    _chk(vpool, "value pool", torch.bfloat16, tuple(kpool.shape))
+    _chk(tiles, "attention tiles", torch.int32)
+    _chk(block_table, "block table", torch.int32)
+    _chk(out, "attention output", torch.bfloat16)
+    if out.numel() != M * nh * hd:
+        raise KernelError(f"attention output of {out.numel()} elements for {M} rows of {nh} heads of {hd}")
+    if tiles.dim() != 2 or tiles.shape[1] != 4:
+        raise KernelError("attention tiles must be [n, 4]")
+    if kpool.dim() != 4 or kpool.shape[2] != page_size or kpool.shape[3] != hd:
+        raise KernelError(f"key pool {tuple(kpool.shape)}, want [pages, kv heads, {page_size}, {hd}]")
+    for name, t in (("distance slopes", slopes), ("sink", sink)):
+        if t is not None:
+            _chk(t, name, torch.float32, (nh,))
+    gate_ptr, gate_ld = c_void_p(0), 0
+    if gate is not None:
+        _chk(gate, "head gate", torch.bfloat16)
+        if gate.dim() != 2 or gate.shape[0] != M or gate_col + nh > gate.shape[1]:
+            raise KernelError(f"head gate of shape {tuple(gate.shape)} holds no {nh} columns from {gate_col} on")
+        gate_ptr, gate_ld = c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    nkv = kpool.shape[1]
+
+    def work():
+        nbytes = flops = 0
+        for _, _, n, p0 in tiles.cpu().tolist():
+            first = max(0, p0 - int(window) + 1) if window else 0
+            pairs = sum((min(p + 1, int(window)) if window else p + 1) + (min(max(p + 1 - int(window), 0), int(keep))
+                                                                          if window else 0) for p in range(p0, p0 + n))
+            nbytes += (p0 + n - first + min(int(keep), first)) * 2 * nkv * hd * 2 + 2 * n * nh * hd * 2
+            flops += 4 * nh * hd * pairs
+        return nbytes, flops
+    check(fn("snk_attention_prefill_tc_split")(
+        _ptr(q), M, _ptr(kpool), _ptr(vpool), kpool.shape[0], _ptr(block_table), block_table.shape[1], page_size,
+        _ptr(tiles), tiles.shape[0], _ptr(out), nh, nkv, hd, int(window or 0), float(scale), int(keep or 0),
+        _ptr(slopes), _ptr(sink), gate_ptr, gate_ld, _stream()), "attention_prefill_tc", work=work)
     return out
 
 

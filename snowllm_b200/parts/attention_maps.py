@@ -105,6 +105,15 @@ def attention_tiles(ctx, tile_rows: int):
     return ctx.memo[key]
 
 
+def single_row_tiles(ctx, rows):
+    """``rows`` (host list of row numbers) as tiles of one row each, int32 [n, 2] on the device; once per step."""
+    key = ("attention_maps_single_rows", len(rows))
+    if key not in ctx.memo:
+        host = torch.tensor([[r, 1] for r in rows], dtype=torch.int32).pin_memory()
+        ctx.memo[key] = host.to(ctx.device, non_blocking=True)
+    return ctx.memo[key]
+
+
 class MapsAttention(Part):
     libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "attention_split", "attention", "sublayer")
     maps = 1
@@ -211,9 +220,39 @@ class MapsAttention(Part):
                                   plain_norm=self.qk_norm_eps is not None and not self.norm_weights,
                                   whole_norm=self.whole_norm)
         ctx.tap("attention_q", q)
-        decode_only = max(ctx.host_seg_len) <= 1
-        tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
-                                                      self.v_head_dim, self.dtype, decode_only)
+        if self._prompt_kernel_ok(ctx, q, cache, out_dtype):
+            # prompt portions on the tcgen05 kernel; the rows of short segments (decoded tokens beside them) below
+            tc_tiles, _, rows_host = plan.split(ctx, kernels.PREFILL_TC_TILE_ROWS)
+            out = torch.empty(ctx.M, self.nq, self.v_head_dim, dtype=out_dtype, device=q.device)
+            kernels.attention_prefill_tc_split(q, kpool, vpool, cache.block_table, cache.page_size, tc_tiles, self.scale,
+                                               out, window=self.window, keep=self.keep_first, slopes=self.slopes,
+                                               sink=self.sink, gate=proj if self._gate_in_kernel() else None,
+                                               gate_col=g_off)
+            if not rows_host:
+                ctx.tap("attention_o", out)
+                return proj, out
+            tiles = single_row_tiles(ctx, rows_host)
+            return proj, self._rows(ctx, q, cache, proj, g_off, out_dtype, tiles, 1, out)
+        return proj, self._rows(ctx, q, cache, proj, g_off, out_dtype, None, None, None)
+
+    def _prompt_kernel_ok(self, ctx, q, cache, out_dtype) -> bool:
+        """Whether the step's long segments go to the tcgen05 prompt kernel: bfloat16, one map, heads of 64 for
+        keys and values alike, a mask and a bias it knows (causal, a window with or without kept first keys, a
+        slope per head, a sink per head, a gate per head)."""
+        return (self.maps == 1 and self.head_dim == 64 and self.v_head_dim == 64 and self.bias is None
+                and self.block is None and self.head_scale is None and out_dtype == torch.bfloat16
+                and kernels.attention_prefill_tc_ok(q, cache.page_size)
+                and max(ctx.host_seg_len) >= plan.PREFILL_MIN_ROWS)
+
+    def _rows(self, ctx, q, cache, proj, g_off, out_dtype, tiles, tile_rows, out):
+        """The kernels of csrc/attention_split.cu: every row of the step (``tiles`` None), or the rows that
+        ``tiles`` names, written into ``out``."""
+        kpool, vpool = cache.pools
+        decode_only = tiles is None and max(ctx.host_seg_len) <= 1
+        if tiles is None:
+            tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
+                                                          self.v_head_dim, self.dtype, decode_only)
+            tiles = attention_tiles(ctx, tile_rows)
         num_chunks, scratch, chunk = 1, None, kernels.SPLIT_ATTENTION_CHUNK
         if decode_only:
             # rows of decoded tokens: their keys in chunks, one block each, merged in chunk order
@@ -225,13 +264,13 @@ class MapsAttention(Part):
                 scratch = ctx.scratch(kernels.attention_scratch_bytes(ctx.M, self.nq, self.v_head_dim, num_chunks))
         out = kernels.split_attention(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
                                       ctx.row_seg, self.scale, maps=self.maps, window=self.window, bias=self.bias,
-                                      tiles=attention_tiles(ctx, tile_rows), tile_rows=tile_rows,
+                                      tiles=tiles, tile_rows=tile_rows, out=out,
                                       out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch, chunk=chunk,
                                       block=self.block, head_scale=self.head_scale, sink=self.sink,
                                       keep=self.keep_first, slopes=self.slopes,
                                       gate=proj if self._gate_in_kernel() else None, gate_col=g_off)
         ctx.tap("attention_o", out)
-        return proj, out
+        return out
 
     def _convolved(self, ctx, proj, cache):
         """(the paged view, the rows split_prepare reads): a kind whose projections pass something on their

@@ -69,6 +69,14 @@ MIXED = config([conv_layer(),
                            mlp=moe(8, 4, 4, 0.7, (24, 3.0)))])
 
 
+# heads of 64 for keys and values: the sizes the tcgen05 prompt kernel takes in bfloat16
+HEADS_OF_64 = config([conv_layer(heads=6, kv_heads=3, dim=64, vdim=64, scale=0.11, window=52, keep_first=10, conv=3,
+                                 rot_dims=16),
+                      slope_layer(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.15, window=170),
+                      conv_layer(heads=2, kv_heads=2, dim=64, vdim=64, scale=0.2, window=150, keep_first=140, conv=2,
+                                 rot_dims=64, mlp=None)], width=64)
+
+
 def draw_weights(cfg: dict, seed: int = 0, dtype=torch.bfloat16) -> dict:
     """name -> tensor (as stored: ``dtype``) from the framework's seeded generator, with the small tensors
     redrawn so that each mechanism carries weight: conv taps of size one, gates and routers whose logits are
