@@ -793,20 +793,36 @@ SNK_API int snk_attention_decode_mma(const void* q, const void* pool, const int*
 // rows are zeroed before use.  For page sizes that divide 256 and are multiples of 8.
 // The wait is bounded by wall time; when it runs out the block records it (snk_attention_decode_status)
 // and goes on without the data.
+// EXTRA: options for mixers that bring more than a causal or windowed softmax (off: 0 or null).  Keys and
+// values in pools of their own [pages, kv heads, page_size, HD] (a second map; k_mul 1, v_add 0); `keep`: a row's
+// kept first keys come in chunks of their own ahead of its window's (chunk_keys, common.cuh); `slopes`:
+// slope[head] * (pos - kp) off the scaled score; `sink`: one more term exp(sink[head]) in the sum of the row's
+// first chunk; `gate`: the head's output times sigmoid(gate[m * gate_ld + head]) (one chunk; with several the
+// merge applies it).
 #define FD_WAIT_NS 1000000000ull
 __device__ int g_fd_status;
 
-template <int HD>
+template <int HD, bool EXTRA>
 __global__ void __launch_bounds__(FA_WARPS * 32)
-attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q,
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_v,
+                            int k_mul, int v_add, const bf16* __restrict__ q,
                             const int* __restrict__ block_table, int max_pages, int page_size,
                             const int* __restrict__ positions, const int* __restrict__ row_seg,
                             const int* __restrict__ row_list, bf16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
-                            int window, int num_chunks, float scale_log2) {
+                            int window, int num_chunks, float scale_log2, int keep,
+                            const float* __restrict__ slopes, const float* __restrict__ sink,
+                            const bf16* __restrict__ gate, long long gate_ld) {
   // the map is a kernel parameter: fetching it does not have to wait for the kernel in front
-  if (threadIdx.x == 0)
+  if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+  }
+  if (!EXTRA) {
+    keep = 0;
+    slopes = sink = nullptr;
+    gate = nullptr;
+  }
   pdl_begin();
   constexpr int CH = HD / 8, KT = HD / 16, NT = HD / 8, PANELS = HD / 64;
   constexpr uint32_t PANEL = FD_CHUNK * 128;              // bytes of one 64-element panel of the chunk's rows
@@ -824,11 +840,21 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int pos = positions[m];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int c = lo / FD_CHUNK + blockIdx.z;
-  if ((long long)c * FD_CHUNK > pos) return;
-  const int k0 = c * FD_CHUNK;
-  const int k_begin = max(lo, k0), k_end = min(pos + 1, k0 + FD_CHUNK);
+  int k0, k_begin, k_end;
+  if (EXTRA) {
+    int first, last;
+    bool inside;
+    if (!chunk_keys(pos, window, keep, FD_CHUNK, (int)blockIdx.z, first, last, k0, inside)) return;
+    k_begin = first;
+    k_end = last + 1;
+  } else {
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int c = lo / FD_CHUNK + blockIdx.z;
+    if ((long long)c * FD_CHUNK > pos) return;
+    k0 = c * FD_CHUNK;
+    k_begin = max(lo, k0);
+    k_end = min(pos + 1, k0 + FD_CHUNK);
+  }
   const int* bt = block_table + (size_t)row_seg[m] * max_pages;
 
   if (threadIdx.x == 0) {
@@ -851,11 +877,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     for (int i = lane; i < n_pages; i += 32) {
       const int page = bt[first_page + i];
       const int row = (first_page + i) * page_size - k0;                    // the page's first row in the chunk
-      const int y_k = ((page * 2) * nkv + kvh) * page_size, y_v = ((page * 2 + 1) * nkv + kvh) * page_size;
+      const int y_k = ((page * k_mul) * nkv + kvh) * page_size, y_v = ((page * k_mul + v_add) * nkv + kvh) * page_size;
 #pragma unroll
       for (int p = 0; p < PANELS; ++p) {
         tma_load_2d(fd_smem + p * PANEL + row * 128, &map_kv, &bar, p * 64, y_k);
-        tma_load_2d(fd_smem + (PANELS + p) * PANEL + row * 128, &map_kv, &bar, p * 64, y_v);
+        tma_load_2d(fd_smem + (PANELS + p) * PANEL + row * 128, &map_v, &bar, p * 64, y_v);
       }
     }
   }
@@ -920,12 +946,19 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
       }
     }
     float mx[2] = {-INFINITY, -INFINITY};
+    float slope2[2] = {0.f, 0.f};                         // this thread's two rows' slopes, in units of log 2
+    if (slopes) {
+      slope2[0] = slopes[kvh * group + min(g, group - 1)] * 1.4426950408889634f;
+      slope2[1] = slopes[kvh * group + min(g + 8, group - 1)] * 1.4426950408889634f;
+    }
 #pragma unroll
     for (int i = 0; i < FA_BK / 8; ++i) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kp = w0 + 8 * i + 2 * t + (j & 1);
-        s[i][j] = (kp >= k_begin && kp < k_end) ? s[i][j] * scale_log2 : -INFINITY;
+        float sv = s[i][j] * scale_log2;
+        if (slopes) sv = fmaf(-slope2[j >> 1], (float)(pos - kp), sv);
+        s[i][j] = (kp >= k_begin && kp < k_end) ? sv : -INFINITY;
         mx[j >> 1] = fmaxf(mx[j >> 1], s[i][j]);
       }
     }
@@ -987,15 +1020,22 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
 #pragma unroll
     for (int w = 0; w < FA_WARPS; ++w) mxl = fmaxf(mxl, ml[(w * 16 + r) * 2]);
     float l = 0.f, o = 0.f;
+    const int head = kvh * group + r;
+    if (sink && blockIdx.z == 0) {                        // the sink: one more term of the sum, without a key
+      const float sk = sink[head] * 1.4426950408889634f;
+      mxl = fmaxf(mxl, sk);
+      l = exp2f(sk - mxl);
+    }
 #pragma unroll
     for (int w = 0; w < FA_WARPS; ++w) {                  // warps in key order
       const float f = exp2f(ml[(w * 16 + r) * 2] - mxl);  // a warp without keys: exp2(-inf) = 0
       l += ml[(w * 16 + r) * 2 + 1] * f;
       o = fmaf(mo[(w * 16 + r) * HD + d], f, o);
     }
-    const int head = kvh * group + r;
     if (num_chunks == 1) {
-      out[((size_t)m * nh + head) * HD + d] = __float2bfloat16_rn(o / l);
+      float v = o / l;
+      if (gate) v /= 1.f + expf(-__bfloat162float(gate[(size_t)m * gate_ld + head]));
+      out[((size_t)m * nh + head) * HD + d] = __float2bfloat16_rn(v);
     } else {
       const size_t slot = ((size_t)blockIdx.x * nh + head) * num_chunks + blockIdx.z;
       part_o[slot * HD + d] = o;
@@ -1014,20 +1054,31 @@ static bool decode_tma_page_ok(int page_size) {
 
 // num_pages: pages in the pool (it is [num_pages, 2, nkv, page_size, hd]).  Page sizes the TMA kernel does
 // not take give SNK_ERR_SIZE (the caller then uses snk_attention_decode_mma).
-SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long num_pages, const int* block_table,
-                                     int max_pages, int page_size, const int* positions, const int* row_seg,
-                                     const int* row_list, void* out, void* scratch, int M, int nh, int nkv,
-                                     int hd, int window, int num_chunks, float scale, cudaStream_t stream) {
+static int fd_launch(const void* q, const void* pool, const void* vpool, long long num_pages, const int* block_table,
+                     int max_pages, int page_size, const int* positions, const int* row_seg,
+                     const int* row_list, void* out, void* scratch, int M, int nh, int nkv,
+                     int hd, int window, int num_chunks, float scale, int keep, const float* slopes,
+                     const float* sink, const void* gate, long long gate_ld, cudaStream_t stream) {
   if (M <= 0) return 0;
+  if (keep < 0 || (keep > 0 && window <= 0)) return SNK_ERR_SIZE;
   if (nkv <= 0 || nh % nkv || nh / nkv > 16 || nkv > 65535 || num_chunks < 1 || num_chunks > 65535)
     return SNK_ERR_SIZE;
   if ((hd != 64 && hd != 128) || !decode_tma_page_ok(page_size) || num_pages <= 0) return SNK_ERR_SIZE;
   if (num_pages * 2 * nkv * page_size >= (1ll << 31)) return SNK_ERR_SIZE;       // row coordinates are 32-bit
   if (num_chunks > 1 && scratch == nullptr) return SNK_ERR_SIZE;
-  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16)) return SNK_ERR_ALIGN;
-  CUtensorMap map;
-  const int rc = tensor_map(pool, num_pages * 2 * nkv * page_size, hd, page_size, 64, &map);
+  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16) || ((uintptr_t)vpool % 16)) return SNK_ERR_ALIGN;
+  // vpool null: keys and values of a page side by side in one pool [pages, 2, kv heads, page_size, hd]
+  const int k_mul = vpool ? 1 : 2, v_add = vpool ? 0 : 1;
+  CUtensorMap map, map_v;
+  int rc = tensor_map(pool, num_pages * k_mul * nkv * page_size, hd, page_size, 64, &map);
   if (rc) return rc;
+  map_v = map;
+  if (vpool) {
+    rc = tensor_map(vpool, num_pages * nkv * page_size, hd, page_size, 64, &map_v);
+    if (rc) return rc;
+  }
+  const bool extra = vpool || keep || slopes || sink || gate;
+  const bf16* gp = static_cast<const bf16*>(gate);
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(M, nkv, num_chunks);
   const size_t smem = 1024 + (size_t)2 * (hd / 64) * FD_CHUNK * 128 + (size_t)16 * hd * 2;
@@ -1035,19 +1086,46 @@ SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long 
   float* part_ml = part_o ? part_o + (size_t)M * nh * num_chunks * hd : nullptr;
   const bf16* qp = static_cast<const bf16*>(q);
   bf16* op = static_cast<bf16*>(out);
+#define FD_LAUNCH(HD_, EXTRA_)                                                                                   \
+  do {                                                                                                           \
+    cudaFuncSetAttribute(attention_decode_tma_kernel<HD_, EXTRA_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                         (int)smem);                                                                             \
+    snk_launch(attention_decode_tma_kernel<HD_, EXTRA_>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map,     \
+               map_v, k_mul, v_add, qp, block_table, max_pages, page_size, positions, row_seg, row_list, op,     \
+               part_o, part_ml, nh, nkv, window, num_chunks, scale_log2, keep, slopes, sink, gp, gate_ld);       \
+  } while (0)
   if (hd == 64) {
-    cudaFuncSetAttribute(attention_decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    snk_launch(attention_decode_tma_kernel<64>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map, qp, block_table,
-               max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv, window, num_chunks,
-               scale_log2);
+    if (extra) FD_LAUNCH(64, true);
+    else FD_LAUNCH(64, false);
   } else {
-    cudaFuncSetAttribute(attention_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    snk_launch(attention_decode_tma_kernel<128>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map, qp, block_table,
-               max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv, window, num_chunks,
-               scale_log2);
+    if (extra) FD_LAUNCH(128, true);
+    else FD_LAUNCH(128, false);
   }
+#undef FD_LAUNCH
   SNK_LAUNCH_CHECK();
   return 0;
+}
+
+SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long num_pages, const int* block_table,
+                                     int max_pages, int page_size, const int* positions, const int* row_seg,
+                                     const int* row_list, void* out, void* scratch, int M, int nh, int nkv,
+                                     int hd, int window, int num_chunks, float scale, cudaStream_t stream) {
+  return fd_launch(q, pool, nullptr, num_pages, block_table, max_pages, page_size, positions, row_seg, row_list, out,
+                   scratch, M, nh, nkv, hd, window, num_chunks, scale, 0, nullptr, nullptr, nullptr, 0, stream);
+}
+
+// The same over keys and values in pools of their own [pages, nkv, page_size, hd], with kept first keys (a row's
+// chunks are then counted as chunk_keys does, and so must the merge), a slope and a sink per head (float [nh])
+// and a gate per (row, head) (bfloat16, gate[m * gate_ld + head]; applied here when there is one chunk).
+SNK_API int snk_attention_decode_tma_split(const void* q, const void* kpool, const void* vpool, long long num_pages,
+                                           const int* block_table, int max_pages, int page_size,
+                                           const int* positions, const int* row_seg, void* out, void* scratch,
+                                           int M, int nh, int nkv, int hd, int window, int num_chunks, float scale,
+                                           int keep, const float* slopes, const float* sink, const void* gate,
+                                           long long gate_ld, cudaStream_t stream) {
+  if (!vpool) return SNK_ERR_SIZE;
+  return fd_launch(q, kpool, vpool, num_pages, block_table, max_pages, page_size, positions, row_seg, nullptr, out,
+                   scratch, M, nh, nkv, hd, window, num_chunks, scale, keep, slopes, sink, gate, gate_ld, stream);
 }
 
 // Queue copies of the two status words (decode, prompt) into ``host`` (pinned host memory, two ints) on

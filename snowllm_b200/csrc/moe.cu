@@ -647,3 +647,31 @@ SNK_API int snk_moe_scaled_rows(const void* x, const int* sorted_pair, const flo
   SNK_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// One logit per row: out[m] = x[m] . w (float), a warp per row (the gate of a shared expert, which every
+// token passes: one number per token).  The order of the sum depends on H alone.
+template <typename T>
+__global__ void row_dot_kernel(const T* __restrict__ x, SmallVec w, float* __restrict__ out, int M, int H, int vec) {
+  pdl_begin();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (m >= M) return;
+  const T* xr = x + (size_t)m * H;
+  const float acc = w.is_f32 ? warp_dot<T, float>(xr, static_cast<const float*>(w.p), H, lane, vec)
+                             : warp_dot<T, bf16>(xr, static_cast<const bf16*>(w.p), H, lane, vec);
+  if (lane == 0) out[m] = acc;
+}
+
+SNK_API int snk_row_dot(const void* x, const void* w, int w_is_f32, float* out, int M, int H, int dtype,
+                        cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0) return SNK_ERR_SIZE;
+  const size_t esz = dtype == SNK_F32 ? 4 : 2, wsz = w_is_f32 ? 4 : 2;
+  const int vec = ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((H * esz) % 16 == 0) && ((H * wsz) % 16 == 0);
+  const int warps = 4;
+  SNK_DISPATCH(dtype, snk_launch(row_dot_kernel<T>, dim3((M + warps - 1) / warps), dim3(warps * 32), 0, stream,
+                                 static_cast<const T*>(x), SmallVec{w, w_is_f32}, out, M, H, vec));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}

@@ -47,6 +47,7 @@ _SIGNATURES = {
         "snk_attention_decode_mma": [P, P, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "snk_attention_prefill_tma": [P, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_tma": [P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
+        "snk_attention_decode_tma_split": [P, P, P, LL, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, LL, P],
         "snk_attention_decode_status": [],
         "snk_attention_decode_status_peek": [P, P],
     },
@@ -85,6 +86,7 @@ _SIGNATURES = {
         "snk_norm_route_sort": [P, P, P, I, P, I, F, P, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, F, I, P, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
         "snk_moe_scaled_rows": [P, P, P, P, P, I, I, I, I, P],
+        "snk_row_dot": [P, P, I, P, I, I, I, P],
     },
     "sublayer": {
         "snk_norm_add": [P, P, P, I, P, I, I, F, I, P],
@@ -728,6 +730,62 @@ def attention_decode_mma(q, pool, block_table, page_size, positions, row_seg, sc
     return out
 
 
+def attention_decode_tma_split(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, num_chunks, out, *,
+                               window=None, keep=0, slopes=None, sink=None, gate=None, gate_col=0, scratch=None):
+    """``attention_decode_mma`` by TMA over keys and values in pools of their own [pages, kv heads, page_size,
+    64 or 128], with the options of ``split_attention``: ``keep`` first positions beside the window (a row's
+    chunks of 256 keys are then the chunks of its kept keys followed by its window's; ``num_chunks`` counts
+    both), ``slopes`` and ``sink`` float [heads], ``gate`` [M, width] bfloat16 whose columns from ``gate_col``
+    hold a logit per head.  Every row of the step stands alone."""
+    M, nh, hd = q.shape
+    _chk(q, "q", torch.bfloat16)
+    _chk(kpool, "key pool", torch.bfloat16)
+    _chk(vpool, "value pool", torch.bfloat16, tuple(kpool.shape))
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    _chk(out, "attention output", torch.bfloat16)
+    if out.numel() != M * nh * hd:
+        raise KernelError(f"attention output of {out.numel()} elements for {M} rows of {nh} heads of {hd}")
+    if kpool.dim() != 4 or kpool.shape[2] != page_size or kpool.shape[3] != hd:
+        raise KernelError(f"key pool {tuple(kpool.shape)}, want [pages, kv heads, {page_size}, {hd}]")
+    for name, t in (("distance slopes", slopes), ("sink", sink)):
+        if t is not None:
+            _chk(t, name, torch.float32, (nh,))
+    gate_ptr, gate_ld = c_void_p(0), 0
+    if gate is not None:
+        _chk(gate, "head gate", torch.bfloat16)
+        if gate.dim() != 2 or gate.shape[0] != M or gate_col + nh > gate.shape[1]:
+            raise KernelError(f"head gate of shape {tuple(gate.shape)} holds no {nh} columns from {gate_col} on")
+        gate_ptr, gate_ld = c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
+    num_chunks = int(num_chunks)
+    if num_chunks > 1:
+        need = attention_scratch_bytes(M, nh, hd, num_chunks)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _chk(scratch, "attention scratch", torch.uint8)
+        if scratch.numel() < need:
+            raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
+    nkv, keep = kpool.shape[1], int(keep or 0)
+
+    def work():
+        pos = positions.cpu().long()
+        keys = (pos + 1).clamp(max=int(window)) if window else pos + 1
+        if keep:
+            keys = keys + (pos + 1 - int(window)).clamp(min=0, max=keep)
+        total = int(keys.sum())
+        return total * 2 * nkv * hd * 2 + 2 * M * nh * hd * 2, 4 * nh * hd * total
+    check(fn("snk_attention_decode_tma_split")(
+        _ptr(q), _ptr(kpool), _ptr(vpool), kpool.shape[0], _ptr(block_table), block_table.shape[1], page_size,
+        _ptr(positions), _ptr(row_seg), _ptr(out), _ptr(scratch), M, nh, nkv, hd, int(window or 0), num_chunks,
+        float(scale), keep, _ptr(slopes), _ptr(sink), gate_ptr, gate_ld, _stream()), "attention_decode_tma", work=work)
+    if num_chunks > 1:
+        check(fn("snk_attention_merge_gated")(_ptr(scratch), _ptr(positions), _ptr(out), M, nh, hd, int(window or 0),
+                                              keep, DECODE_MMA_CHUNK, num_chunks, gate_ptr, gate_ld, BF16, _stream()),
+              "attention_merge", work=lambda: (M * nh * (hd + 2) * 4 * num_chunks + M * nh * hd * 2, 0))
+    return out
+
+
 class StatusWatch:
     """The error words of the kernels whose waits are bounded (TMA and tcgen05 kernels: a wait that runs out
     makes the block give up, and its rows of the output are then not to be trusted), read where the host
@@ -1173,6 +1231,20 @@ def norm_route_sort(residual, delta, gamma, eps, dtype, router_w, bias, top_k, n
         work=lambda: (2 * M * H * 4 + _nbytes(x, router_w, ints, wts) + (_nbytes(delta) if delta is not None else 0)
                       + (moe.weights.shape[1] * M * H * 4 if moe else 0), 2 * M * E * H))
     return x, ids, wts, offsets, pair_pos, sorted_pair
+
+
+def row_dot(x, w):
+    """One float logit per row: ``x`` [M, H] (compute dtype) . ``w`` [H] or [1, H] (float32 or the compute dtype);
+    returns float [M, 1]."""
+    M, H = x.shape
+    _chk(x, "row gate input", (torch.float32, torch.bfloat16))
+    w32 = _small(w, "row gate weight", x.dtype)
+    if w.numel() != H:
+        raise KernelError(f"row gate weight of {w.numel()} elements for rows of {H}")
+    out = torch.empty(M, 1, dtype=torch.float32, device=x.device)
+    check(fn("snk_row_dot")(_ptr(x), _ptr(w), w32, _ptr(out), M, H, code_of(x.dtype), _stream()), "row_dot",
+          work=lambda: (_nbytes(x, w, out), 2 * M * H))
+    return out
 
 
 def moe_sort(topk_ids, num_experts):

@@ -244,11 +244,36 @@ class MapsAttention(Part):
                 and kernels.attention_prefill_tc_ok(q, cache.page_size)
                 and max(ctx.host_seg_len) >= plan.PREFILL_MIN_ROWS)
 
+    def _decode_kernel_ok(self, q, cache, out_dtype) -> bool:
+        """Whether rows that stand alone go to the TMA decode kernel: bfloat16, one map, heads of 64 or 128 for
+        keys and values alike, up to 16 heads per kv head, a mask and a bias it knows."""
+        return (self.maps == 1 and self.head_dim == self.v_head_dim and self.head_dim in kernels.PREFILL_HEAD_DIMS
+                and self.bias is None and self.block is None and self.head_scale is None
+                and out_dtype == torch.bfloat16 and q.dtype == torch.bfloat16
+                and self.nq // self.num_kv_heads <= kernels.DECODE_MMA_MAX_GROUP
+                and kernels.DECODE_TMA and kernels.decode_tma_page_ok(cache.page_size))
+
     def _rows(self, ctx, q, cache, proj, g_off, out_dtype, tiles, tile_rows, out):
         """The kernels of csrc/attention_split.cu: every row of the step (``tiles`` None), or the rows that
         ``tiles`` names, written into ``out``."""
         kpool, vpool = cache.pools
         decode_only = tiles is None and max(ctx.host_seg_len) <= 1
+        if decode_only and self._decode_kernel_ok(q, cache, out_dtype):
+            # rows of decoded tokens on the tensor cores, their keys and values by TMA in chunks of 256
+            chunk = kernels.DECODE_MMA_CHUNK
+            num_chunks = plan.chunks(ctx, self.window, None, chunk, keep=self.keep_first)
+            if self.window:                # a captured step plans for its longest sequence; a window spans fewer
+                num_chunks = min(num_chunks, (self.window - 1) // chunk + 2 + -(-self.keep_first // chunk))
+            scratch = ctx.scratch(kernels.attention_scratch_bytes(ctx.M, self.nq, self.v_head_dim, num_chunks)) \
+                if num_chunks > 1 else None
+            out = torch.empty(ctx.M, self.nq, self.v_head_dim, dtype=out_dtype, device=q.device)
+            kernels.attention_decode_tma_split(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
+                                               ctx.row_seg, self.scale, num_chunks, out, window=self.window,
+                                               keep=self.keep_first, slopes=self.slopes, sink=self.sink,
+                                               gate=proj if self._gate_in_kernel() else None, gate_col=g_off,
+                                               scratch=scratch)
+            ctx.tap("attention_o", out)
+            return out
         if tiles is None:
             tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
                                                           self.v_head_dim, self.dtype, decode_only)

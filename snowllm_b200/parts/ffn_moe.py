@@ -102,10 +102,7 @@ class SigmoidMoE(Part):
                                else torch.cat((tensors["shared_gate"], tensors["shared_up"]), 0).contiguous())
             self.shared_w2 = tensors["shared_down"]
             if self.shared.get("row_gate"):
-                # the one gate row as a product of its own (rows padded to what the products take); its float
-                # output's first column is the logit
-                g = tensors["shared_row_gate"]
-                self.shared_row_gate = torch.cat((g, g.new_zeros(15, g.shape[1])), 0).contiguous()
+                self.shared_row_gate = tensors["shared_row_gate"].contiguous()
 
     def bytes_read(self, bound, picked=None):
         """Router and bias whole; of the experts only those that were picked (``picked`` None: all)."""
@@ -147,7 +144,7 @@ class SigmoidMoE(Part):
         act = linear_glu(x, self.shared_w13, self.shared_interleaved, self.activation, self.shared["limit"])
         gate = None
         if self.shared_row_gate is not None:
-            gate = linear(x, self.shared_row_gate, out_dtype=torch.float32)
+            gate = kernels.row_dot(x, self.shared_row_gate)        # float [M, 1]: one logit per token
             if ctx is not None:
                 ctx.tap("shared_row_gate", gate)
         return kernels.DeltaSum(linear(act, self.shared_w2, out_dtype=torch.float32), routed, a_gate=gate)

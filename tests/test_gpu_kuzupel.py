@@ -265,7 +265,62 @@ def test_prompt_kernel_on_tensor_memory_sees_its_window_and_the_kept_first_keys(
     share = (lambda row, head: 1.0) if gate is None else (lambda row, head: float(torch.sigmoid(gate_r[row, head])))
     if window:
         assert float((got[inside, 1] - share(inside, 1) * v[edge_in, 0].double()).abs().max()) < 0.05
-        assert float((got[outside, 2] - share(outside, 2) * v[edge_out, 1].double()).abs().max()) > 0.1 * share(outside, 2)
+        if edge_out >= keep:                                                 # not one of the kept keys
+            assert float((got[outside, 2] - share(outside, 2) * v[edge_out, 1].double()).abs().max()) > 0.1 * share(outside, 2)
+    if keep:
+        assert float((got[699, 3] - share(699, 3) * v[keep - 1, 1].double()).abs().max()) < 0.05
+        if keep < 690 - window + 1:
+            assert float((got[690, 0] - share(690, 0) * v[keep, 0].double()).abs().max()) > 0.1 * share(690, 0)
+
+
+@pytest.mark.parametrize("P", [16, 64])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("window,keep", [(77, 5), (21, 300), (130, 0), (600, 290), (None, 0)])
+@pytest.mark.parametrize("plain_softmax", [False, True])
+def test_decode_kernel_by_tma_sees_its_window_and_the_kept_first_keys(P, d, window, keep, plain_softmax):
+    """Rows that stand alone (every position of a sequence as its own row) on the TMA decode kernel: chunks of
+    256 keys, the kept first keys in chunks of their own, merged in order."""
+    from snowllm_b200.ops import kernels
+    g = torch.Generator().manual_seed(13)
+    T, H, G = 700, 4, 2
+    dtype = torch.bfloat16
+    q = torch.randn(T, H, d, generator=g).to(dtype)
+    k = (torch.randn(T, G, d, generator=g) * 0.05).to(dtype)
+    v = torch.randn(T, G, d, generator=g).to(dtype)
+    gate = None if plain_softmax else torch.randn(T, H, generator=g) * 2
+    slopes = None if plain_softmax else torch.tensor([0.01, 0.0, 0.02, 0.003])
+    inside, outside = 650, 640
+    boost = 96.0 / d
+    if window:
+        edge_in, edge_out = inside - window + 1, outside - window
+        k[edge_in, 0] = (q[inside, 1].float() * boost).to(dtype)
+        k[edge_out, 1] = (q[outside, 2].float() * boost).to(dtype)
+    if keep:
+        k[keep - 1, 1] = (q[699, 3].float() * boost).to(dtype)
+        k[keep, 0] = (q[690, 0].float() * boost).to(dtype)
+    kpool, vpool, table = paged(k, v, P, dtype, g)
+    positions = torch.arange(T, dtype=torch.int32, device="cuda")
+    most = 0
+    for pos in range(T):
+        lo = max(0, pos - window + 1) if window else 0
+        most = max(most, -(-min(keep, lo) // 256) + pos // 256 - lo // 256 + 1)
+    out = torch.empty(T, H, d, dtype=dtype, device="cuda")
+    kernels.attention_decode_tma_split(q.cuda(), kpool, vpool, table, P, positions, torch.zeros_like(positions), 0.25,
+                                       most, out, window=window, keep=keep,
+                                       slopes=None if slopes is None else slopes.cuda(),
+                                       sink=None if plain_softmax else torch.zeros(H, device="cuda"),
+                                       gate=None if gate is None else gate.to(dtype).cuda().contiguous())
+    assert kernels.attention_decode_status() == 0
+    got = out.cpu().double()
+    gate_r = None if gate is None else gate.to(dtype).double()
+    want = plain_attention(q.double(), k.double(), v.double(), 0.25, window, keep,
+                           None if slopes is None else slopes.double(), not plain_softmax, gate_r)
+    assert float((got - want).abs().max()) < 3e-2
+    share = (lambda row, head: 1.0) if gate is None else (lambda row, head: float(torch.sigmoid(gate_r[row, head])))
+    if window:
+        assert float((got[inside, 1] - share(inside, 1) * v[edge_in, 0].double()).abs().max()) < 0.05
+        if edge_out >= keep:                                                 # not one of the kept keys
+            assert float((got[outside, 2] - share(outside, 2) * v[edge_out, 1].double()).abs().max()) > 0.1 * share(outside, 2)
     if keep:
         assert float((got[699, 3] - share(699, 3) * v[keep - 1, 1].double()).abs().max()) < 0.05
         if keep < 690 - window + 1:
