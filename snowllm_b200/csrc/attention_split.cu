@@ -152,6 +152,134 @@ __global__ void split_prepare_kernel(const T* __restrict__ proj, long long ld, i
   }
 }
 
+// The same for rows of 16-byte vectors: a block takes one row, a thread IT vectors of it (all of their loads in
+// flight before the first is used), the lanes of a head sit side by side in a warp (dk / VEC of them, a power of
+// two), so that the head's sum of squares and the rotation partner (rot_dim / 2 elements away: a whole number of
+// vectors) come by shuffles; the sum over a whole projection goes through the block; the row's sines and cosines
+// are worked out once, in shared memory.
+template <typename T, int IT>
+__global__ void __launch_bounds__(256)
+split_prepare_vec_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
+                         const float* __restrict__ proj_bias, SmallVec q_gamma, SmallVec k_gamma, int has_norm,
+                         float eps, const float* __restrict__ inv_freq, int rot_dim, float rot_mult,
+                         const int* __restrict__ positions, const int* __restrict__ row_seg,
+                         const int* __restrict__ block_table, int max_pages, int page_size,
+                         T* __restrict__ kpool, T* __restrict__ vpool, T* __restrict__ q_out,
+                         int nq, int nkh, int nkv, int dk, int dv, int write_kv) {
+  pdl_begin();
+  constexpr int VEC = SaVec<T>::N;
+  __shared__ float red[33];
+  extern __shared__ float2 sp_tab[];                   // [rot_dim / 2] (cos, sin) of the row's angles
+  const int m = blockIdx.x;
+  const int lph = dk / VEC, vph = dv / VEC;            // vectors per head of q and k, and of v
+  const int nqv = nq * lph, nkv_ = write_kv ? nkh * lph : 0, nvv = write_kv ? nkv * vph : 0;
+  const int total = nqv + nkv_ + nvv;
+  const T* row = proj + (size_t)m * ld;
+  const int pos = positions[m];
+  const int half = rot_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    sp_tab[i] = make_float2(cs * rot_mult, sn * rot_mult);
+  }
+  uint4 raw[IT];
+  int col[IT];                                         // the vector's first column in the projection
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    col[it] = -1;
+    if (v < total) {
+      col[it] = v < nqv ? q_off + v * VEC : (v < nqv + nkv_ ? k_off + (v - nqv) * VEC : v_off + (v - nqv - nkv_) * VEC);
+      raw[it] = *reinterpret_cast<const uint4*>(row + col[it]);
+    }
+  }
+  float x[IT][VEC];
+  float sq = 0.f, sk = 0.f;                            // this thread's share of the sums over all of q and all of k
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) x[it][e] = 0.f;
+    if (col[it] >= 0) {
+      SaVec<T>::unpack(raw[it], x[it]);
+      if (proj_bias) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[it][e] += proj_bias[col[it] + e];
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss = fmaf(x[it][e], x[it][e], ss);
+      if (v < nqv) sq += ss;
+      else if (v < nqv + nkv_) sk += ss;
+    }
+  }
+  float inv_q = 1.f, inv_k = 1.f;
+  if (has_norm == 2) {
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    inv_q = 1.f / sqrtf(sq / (float)(nq * dk) + eps);
+    inv_k = nkv_ ? 1.f / sqrtf(sk / (float)(nkh * dk) + eps) : 1.f;
+  } else {
+    __syncthreads();                                   // the table of angles is written
+  }
+  const int lane = threadIdx.x & 31;
+  int page = 0;
+  if (write_kv) page = block_table[(size_t)row_seg[m] * max_pages + pos / page_size];
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int v = threadIdx.x + it * blockDim.x;
+    const bool is_q = v < nqv, is_k = !is_q && v < nqv + nkv_, is_v = !is_q && !is_k && v < total;
+    const int hv = is_q ? v : v - nqv;                 // vector within the q (or k) region
+    const int h = hv / lph, li = hv - h * lph;         // head, vector of the head
+    float inv = 1.f;
+    if (has_norm == 1) {                               // a head's own root mean square: every lane takes part
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss = fmaf(x[it][e], x[it][e], ss);
+      for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      inv = 1.f / sqrtf(ss / (float)dk + eps);
+    } else if (has_norm == 2) {
+      inv = is_q ? inv_q : inv_k;
+    }
+    if ((is_q || is_k) && has_norm) {
+      const SmallVec& g = is_q ? q_gamma : k_gamma;
+      const size_t g0 = (has_norm == 2 ? (size_t)h * dk : 0) + (size_t)li * VEC;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x[it][e] = x[it][e] * inv * (g.p ? g[g0 + e] : 1.f);
+    }
+    if (rot_dim > 0) {                                 // the partner half a rotation away: every lane takes part
+      const int d0 = li * VEC, hvn = half / VEC;
+      const bool low = d0 < half, turns = (is_q || is_k) && d0 < rot_dim;
+      const int src = turns ? (low ? lane + hvn : lane - hvn) : lane;
+      float y[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) y[e] = __shfl_sync(0xffffffffu, x[it][e], src);
+      if (turns) {
+        const int i0 = low ? d0 : d0 - half;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float2 cs = sp_tab[i0 + e];
+          x[it][e] = low ? x[it][e] * cs.x - y[e] * cs.y : x[it][e] * cs.x + y[e] * cs.y;
+        }
+      }
+    }
+    if (!(is_q || is_k || is_v)) continue;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)m * nq + h) * dk + li * VEC;
+    } else if (is_k) {
+      const int maps = nkh / nkv;
+      dst = kpool + ((((size_t)page * nkv + h / maps) * page_size + pos % page_size) * maps + h % maps) * dk + li * VEC;
+    } else {
+      const int vv = v - nqv - nkv_;
+      const int hh = vv / vph, lv = vv - hh * vph;
+      dst = vpool + (((size_t)page * nkv + hh) * page_size + pos % page_size) * dv + lv * VEC;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; e += 4) store4<T>(dst + e, x[it][e], x[it][e + 1], x[it][e + 2], x[it][e + 3]);
+  }
+}
+
 SNK_API int snk_split_prepare(const void* proj, long long ld, int q_off, int k_off, int v_off,
                               const float* proj_bias, const void* q_gamma,
                               const void* k_gamma, int gamma_f32, int has_norm, float eps, const float* inv_freq,
@@ -162,6 +290,36 @@ SNK_API int snk_split_prepare(const void* proj, long long ld, int q_off, int k_o
   if (M <= 0) return 0;
   if (nq <= 0 || dk <= 0 || rot_dim < 0 || rot_dim > dk || (rot_dim & 1)) return SNK_ERR_SIZE;
   if (write_kv && (nkv <= 0 || nkh <= 0 || nkh % nkv || dv <= 0)) return SNK_ERR_SIZE;
+  {
+    // rows of 16-byte vectors whose heads' lanes fit a warp: the vector kernel
+    const int vec = dtype == SNK_F32 ? 4 : 8;
+    const size_t esz = dtype == SNK_F32 ? 4 : 2;
+    const int lph = dk / vec;
+    const int total = (nq * dk + (write_kv ? nkh * dk + nkv * dv : 0)) / vec;
+    const bool fits = dk % vec == 0 && lph >= 1 && lph <= 32 && (lph & (lph - 1)) == 0 && (dv % vec == 0 || !write_kv) &&
+                      (rot_dim / 2) % vec == 0 && q_off % vec == 0 && (!write_kv || (k_off % vec == 0 && v_off % vec == 0)) &&
+                      ld % vec == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+                      (!write_kv || ((uintptr_t)kpool % 16 == 0 && (uintptr_t)vpool % 16 == 0)) && total <= 256 * 8 &&
+                      (rot_dim == 0 || inv_freq != nullptr) && esz * vec == 16;
+    if (fits && M <= 2147483647) {
+      const int iters = (total + 255) / 256;
+      const size_t tab = (size_t)(rot_dim / 2) * sizeof(float2);
+#define SP_VEC(I_)                                                                                            \
+  snk_launch(split_prepare_vec_kernel<T, I_>, dim3(M), dim3(256), tab, stream, static_cast<const T*>(proj), ld,    \
+             q_off, k_off, v_off, proj_bias, SmallVec{q_gamma, gamma_f32}, SmallVec{k_gamma, gamma_f32}, has_norm,  \
+             eps, inv_freq, rot_dim, rot_mult, positions, row_seg, block_table, max_pages, page_size,            \
+             static_cast<T*>(kpool), static_cast<T*>(vpool), static_cast<T*>(q_out), nq, nkh, nkv, dk, dv, write_kv)
+      SNK_DISPATCH(dtype, {
+        if (iters <= 1) SP_VEC(1);
+        else if (iters <= 2) SP_VEC(2);
+        else if (iters <= 4) SP_VEC(4);
+        else SP_VEC(8);
+      });
+#undef SP_VEC
+      SNK_LAUNCH_CHECK();
+      return 0;
+    }
+  }
   const int units = nq + (write_kv ? nkh + nkv : 0);
   const int warps = units < 8 ? units : 8;
   dim3 grid(M, (units + warps - 1) / warps);

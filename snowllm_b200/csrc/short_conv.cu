@@ -374,6 +374,83 @@ __global__ void causal_conv_decode_kernel(const T* __restrict__ u, long long ld,
     if (j < L - 1) st[(size_t)j * C + c] = j + 1 < L - 1 ? hist[j + 1] : cur;
 }
 
+// Many rows (prompt portions): as short_conv_strip_kernel above, without the gates.  A thread owns four
+// consecutive channels and walks CONV_STRIP consecutive rows with the last L-1 values in registers; every load
+// of the strip and of the L-1 rows before it is issued before the first value is used.
+template <typename T, int L>
+__global__ void __launch_bounds__(128)
+causal_conv_strip_kernel(const T* __restrict__ u, long long ld, SmallVec w, const T* __restrict__ state,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
+                         const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
+                         T* __restrict__ out, long long out_ld, int M, int C) {
+  pdl_begin();
+  constexpr int VEC = ConvVec<T>::N;
+  using Raw = typename ConvVec<T>::Raw;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (c0 >= C) return;
+  const int m_begin = blockIdx.y * CONV_STRIP;
+  Raw rx[CONV_STRIP], px[L - 1];
+  int sgs[CONV_STRIP];
+#pragma unroll
+  for (int r = 0; r < CONV_STRIP; ++r) {
+    if (m_begin + r < M) {
+      rx[r] = *reinterpret_cast<const Raw*>(u + (size_t)(m_begin + r) * ld + c0);
+      sgs[r] = row_seg[m_begin + r];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < L - 1; ++i) {                  // the rows before the strip: used if they are of its segment
+    const int mm = m_begin - (L - 1) + i;
+    if (mm >= 0) px[i] = *reinterpret_cast<const Raw*>(u + (size_t)mm * ld + c0);
+  }
+  float taps[L][VEC];
+#pragma unroll
+  for (int j = 0; j < L; ++j)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) taps[j][e] = w[(size_t)(c0 + e) * L + j];
+  float hist[L - 1][VEC];                            // hist[0] is the oldest of the L-1 values before the row
+  int seg = -1;
+#pragma unroll
+  for (int r = 0; r < CONV_STRIP; ++r) {
+    const int m = m_begin + r;
+    if (m < M) {
+      const int sg = sgs[r];
+      if (r == 0 || sg != seg) {                     // (re)build the window: rows of this step, else the state
+        seg = sg;
+        const int t = m - cu_seqlens[sg];            // > 0 only at r == 0: a new segment starts at t == 0
+        const bool has_state = seg_start[sg] > 0;
+        const T* st = state + (size_t)seg_slot[sg] * (L - 1) * C;
+#pragma unroll
+        for (int i = 0; i < L - 1; ++i) {
+          const int s = t - (L - 1) + i;             // index into this step's rows; < 0: history
+          if (s >= 0) {                              // then r == 0 and the row is m_begin - (L-1) + i
+            ConvVec<T>::unpack(px[i], hist[i]);
+          } else if (has_state) {
+            ConvVec<T>::unpack(*reinterpret_cast<const Raw*>(st + (size_t)(s + L - 1) * C + c0), hist[i]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) hist[i][e] = 0.f;
+          }
+        }
+      }
+      float x[VEC], y[VEC];
+      ConvVec<T>::unpack(rx[r], x);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float acc = 0.f;                             // taps in order: oldest first, the current token last
+#pragma unroll
+        for (int i = 0; i < L - 1; ++i) acc = fmaf(taps[i][e], hist[i][e], acc);
+        acc = fmaf(taps[L - 1][e], x[e], acc);
+        y[e] = acc;
+#pragma unroll
+        for (int i = 0; i < L - 2; ++i) hist[i][e] = hist[i + 1][e];
+        if (L > 1) hist[L - 2 < 0 ? 0 : L - 2][e] = x[e];
+      }
+      *reinterpret_cast<Raw*>(out + (size_t)m * out_ld + c0) = ConvVec<T>::pack(y);
+    }
+  }
+}
+
 SNK_API int snk_causal_conv(const void* u, long long ld, const void* w, int w_is_f32, void* state,
                             const int* cu_seqlens, const int* seg_start, const int* seg_slot, const int* row_seg,
                             void* out, long long out_ld, int M, int B, int C, int L, int dtype,
@@ -390,11 +467,30 @@ SNK_API int snk_causal_conv(const void* u, long long ld, const void* w, int w_is
     SNK_LAUNCH_CHECK();
     return 0;
   }
-  if (M > 65535) return SNK_ERR_SIZE;
-  dim3 grid((C + threads - 1) / threads, M);
-  SNK_DISPATCH(dtype, snk_launch(causal_conv_kernel<T>, dim3(grid), dim3(threads), 0, stream,
-                                 static_cast<const T*>(u), ld, wv, static_cast<const T*>(state), cu_seqlens,
-                                 seg_start, seg_slot, row_seg, static_cast<T*>(out), out_ld, C, L));
+  const size_t vbytes = dtype == SNK_F32 ? 16 : 8;   // four channels per thread
+  const size_t esz = dtype == SNK_F32 ? 4 : 2;
+  const bool aligned = C % 4 == 0 && (uintptr_t)u % vbytes == 0 && (uintptr_t)state % vbytes == 0 &&
+                       (uintptr_t)out % vbytes == 0 && (ld * esz) % vbytes == 0 && (out_ld * esz) % vbytes == 0;
+  if (L >= 2 && L <= CONV_FAST_L && aligned && M >= 4 * CONV_STRIP) {
+    dim3 sgrid((C / 4 + threads - 1) / threads, (M + CONV_STRIP - 1) / CONV_STRIP);
+    if (sgrid.y > 65535u) return SNK_ERR_SIZE;
+#define CAUSAL_STRIP_LAUNCH(L_)                                                                          \
+    snk_launch(causal_conv_strip_kernel<T, L_>, dim3(sgrid), dim3(threads), 0, stream,                   \
+               static_cast<const T*>(u), ld, wv, static_cast<const T*>(state), cu_seqlens, seg_start,    \
+               seg_slot, row_seg, static_cast<T*>(out), out_ld, M, C)
+    SNK_DISPATCH(dtype, {
+      if (L == 2) CAUSAL_STRIP_LAUNCH(2);
+      else if (L == 3) CAUSAL_STRIP_LAUNCH(3);
+      else CAUSAL_STRIP_LAUNCH(4);
+    });
+#undef CAUSAL_STRIP_LAUNCH
+  } else {
+    if (M > 65535) return SNK_ERR_SIZE;
+    dim3 grid((C + threads - 1) / threads, M);
+    SNK_DISPATCH(dtype, snk_launch(causal_conv_kernel<T>, dim3(grid), dim3(threads), 0, stream,
+                                   static_cast<const T*>(u), ld, wv, static_cast<const T*>(state), cu_seqlens,
+                                   seg_start, seg_slot, row_seg, static_cast<T*>(out), out_ld, C, L));
+  }
   SNK_LAUNCH_CHECK();
   if (L > 1) {
     dim3 sgrid((C + threads - 1) / threads, B);

@@ -349,13 +349,16 @@ def test_attention_kernel_slopes_without_extra_term_or_gate(dtype, mode):
     assert float((want[:, 1] - free[:, 1]).abs().max()) > 0.05
 
 
+# (dk, dv, columns before q): sizes the scalar kernel takes, and rows of 16-byte vectors (the vector kernel; with
+# 48 heads a thread holds several vectors and the sum over the projection crosses warps)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_prepare_normalises_over_the_whole_projection(dtype):
+@pytest.mark.parametrize("H,G,dk,dv,lead", [(5, 2, 10, 6, 2), (5, 1, 16, 8, 8), (48, 12, 64, 32, 0)])
+def test_prepare_normalises_over_the_whole_projection(dtype, H, G, dk, dv, lead):
     from snowllm_b200.ops import kernels
     g = torch.Generator().manual_seed(9)
-    M, H, G, dk, dv, P = 9, 5, 2, 10, 6, 4
-    width = 2 + H * dk + G * dk + G * dv + 3
-    q_off, k_off, v_off = 2, 2 + H * dk, 2 + H * dk + G * dk
+    M, P = 9, 4
+    width = lead + H * dk + G * dk + G * dv + (3 if lead == 2 else 8)
+    q_off, k_off, v_off = lead, lead + H * dk, lead + H * dk + G * dk
     proj = torch.randn(M, width, generator=g).to(dtype)
     proj[:, q_off:q_off + dk] *= 5                                         # one head far larger than the others
     wq, wk = (1 + 0.3 * torch.randn(H * dk, generator=g)).to(dtype), (1 + 0.3 * torch.randn(G * dk, generator=g)).to(dtype)
@@ -370,7 +373,7 @@ def test_prepare_normalises_over_the_whole_projection(dtype):
     full = proj.double()
     want_q = (plain.rms(full[:, q_off:k_off], 1e-3) * wq.double()).view(M, H, dk)
     want_k = (plain.rms(full[:, k_off:v_off], 1e-3) * wk.double()).view(M, G, dk)
-    assert float((q.cpu().double() - want_q).abs().max()) < tol
+    assert float((q.cpu().double() - want_q).abs().max()) < tol * max(1.0, float(want_q.abs().max()) / 4)
     per_head = plain.rms(full[:, q_off:k_off].view(M, H, dk), 1e-3)
     assert float((per_head - want_q).abs().max()) > 0.3                    # a norm per head is another thing
     for m in range(M):
@@ -395,7 +398,7 @@ def run_conv(rows, C, w, cuts, slot, state):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("C,L,extra", [(24, 4, 5), (7, 2, 0), (130, 7, 3), (16, 1, 0)])
+@pytest.mark.parametrize("C,L,extra", [(24, 4, 5), (7, 2, 0), (130, 7, 3), (16, 1, 0), (64, 4, 8), (40, 3, 0), (8, 2, 0)])
 def test_conv_kernel_carries_its_history_and_starts_fresh_in_a_used_slot(dtype, C, L, extra):
     """Fed whole, in portions down to one and two tokens (shorter than the taps), and token by token; the slot
     holds another request's history beforehand; columns beyond the convolved ones are left alone."""
