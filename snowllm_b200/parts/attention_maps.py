@@ -411,6 +411,7 @@ class SinkAttention(MapsAttention):
 class SlopeAttention(MapsAttention):
     """One map per head, no rotation; q and k over one root mean square each, taken over all heads at once;
     a distance penalty slope[h] * (i - j) with slope[h] = 2^(-slope_range * (h + 1) / heads)."""
+    libraries = MapsAttention.libraries + ("attention_tc", "attention_mma")
     whole_norm = True
 
     def __init__(self, dtype, names, *, slope_range: float = 8.0, **kw):
@@ -430,6 +431,7 @@ class SlopeAttention(MapsAttention):
 
 class ConvGateAttention(MapsAttention):
     """Convolved projections, kept first positions, one more term in the softmax's sum, gated heads."""
+    libraries = MapsAttention.libraries + ("attention_tc", "attention_mma", "short_conv")
 
     def __init__(self, dtype, names, *, conv_taps: int | None = None, one_more: bool = True, **kw):
         super().__init__(dtype, names, **kw)
