@@ -341,10 +341,11 @@ SNK_API int snk_attention_merge(const void* scratch, const int* positions, void*
 }
 
 // The merge for rows with kept first keys (their chunks as chunk_keys counts them) and a gate per head:
-// gate (may be null) points at the first head's logit of row 0, in the output's dtype, row pitch gate_ld.
+// gate (may be null) points at the first head's logit of row 0, in the output's dtype, row pitch gate_ld;
+// row_list (may be null): the M rows of the batch that were served.
 SNK_API int snk_attention_merge_gated(const void* scratch, const int* positions, void* out, int M, int nh, int hd,
                                       int window, int keep, int chunk, int num_chunks, const void* gate,
-                                      long long gate_ld, int dtype, cudaStream_t stream) {
+                                      long long gate_ld, int dtype, const int* row_list, cudaStream_t stream) {
   if (M <= 0 || num_chunks <= 1) return 0;
   const float* part_o = static_cast<const float*>(scratch);
   const float* part_ml = part_o + (size_t)M * nh * num_chunks * hd;
@@ -353,7 +354,7 @@ SNK_API int snk_attention_merge_gated(const void* scratch, const int* positions,
   SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads),
                                  (size_t)MERGE_ZG * hd * sizeof(float), stream,
                                  part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window, chunk, num_chunks,
-                                 static_cast<const int*>(nullptr), keep, static_cast<const T*>(gate), gate_ld));
+                                 row_list, keep, static_cast<const T*>(gate), gate_ld));
   SNK_LAUNCH_CHECK();
   return 0;
 }

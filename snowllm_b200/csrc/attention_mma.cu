@@ -1117,14 +1117,15 @@ SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long 
 // The same over keys and values in pools of their own [pages, nkv, page_size, hd], with kept first keys (a row's
 // chunks are then counted as chunk_keys does, and so must the merge), a slope and a sink per head (float [nh])
 // and a gate per (row, head) (bfloat16, gate[m * gate_ld + head]; applied here when there is one chunk).
+// row_list (may be null): the M rows of the batch to serve, when not all of them.
 SNK_API int snk_attention_decode_tma_split(const void* q, const void* kpool, const void* vpool, long long num_pages,
                                            const int* block_table, int max_pages, int page_size,
-                                           const int* positions, const int* row_seg, void* out, void* scratch,
-                                           int M, int nh, int nkv, int hd, int window, int num_chunks, float scale,
-                                           int keep, const float* slopes, const float* sink, const void* gate,
-                                           long long gate_ld, cudaStream_t stream) {
+                                           const int* positions, const int* row_seg, const int* row_list, void* out,
+                                           void* scratch, int M, int nh, int nkv, int hd, int window, int num_chunks,
+                                           float scale, int keep, const float* slopes, const float* sink,
+                                           const void* gate, long long gate_ld, cudaStream_t stream) {
   if (!vpool) return SNK_ERR_SIZE;
-  return fd_launch(q, kpool, vpool, num_pages, block_table, max_pages, page_size, positions, row_seg, nullptr, out,
+  return fd_launch(q, kpool, vpool, num_pages, block_table, max_pages, page_size, positions, row_seg, row_list, out,
                    scratch, M, nh, nkv, hd, window, num_chunks, scale, keep, slopes, sink, gate, gate_ld, stream);
 }
 

@@ -40,14 +40,14 @@ _SIGNATURES = {
         "snk_paged_attention": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "snk_paged_attention_rows": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
         "snk_attention_merge": [P, P, P, I, I, I, I, I, I, I, P, P],
-        "snk_attention_merge_gated": [P, P, P, I, I, I, I, I, I, I, P, LL, I, P],
+        "snk_attention_merge_gated": [P, P, P, I, I, I, I, I, I, I, P, LL, I, P, P],
     },
     "attention_mma": {
         "snk_attention_prefill": [P, P, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_mma": [P, P, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "snk_attention_prefill_tma": [P, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_tma": [P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
-        "snk_attention_decode_tma_split": [P, P, P, LL, P, I, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, LL, P],
+        "snk_attention_decode_tma_split": [P, P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, LL, P],
         "snk_attention_decode_status": [],
         "snk_attention_decode_status_peek": [P, P],
     },
@@ -731,13 +731,19 @@ def attention_decode_mma(q, pool, block_table, page_size, positions, row_seg, sc
 
 
 def attention_decode_tma_split(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, num_chunks, out, *,
-                               window=None, keep=0, slopes=None, sink=None, gate=None, gate_col=0, scratch=None):
+                               window=None, keep=0, slopes=None, sink=None, gate=None, gate_col=0, scratch=None,
+                               rows=None):
     """``attention_decode_mma`` by TMA over keys and values in pools of their own [pages, kv heads, page_size,
     64 or 128], with the options of ``split_attention``: ``keep`` first positions beside the window (a row's
     chunks of 256 keys are then the chunks of its kept keys followed by its window's; ``num_chunks`` counts
     both), ``slopes`` and ``sink`` float [heads], ``gate`` [M, width] bfloat16 whose columns from ``gate_col``
-    hold a logit per head.  Every row of the step stands alone."""
+    hold a logit per head.  Every served row stands alone; ``rows`` (int32, on the device): the rows of the
+    step to serve, when not all of them (the others' outputs are left as they are)."""
     M, nh, hd = q.shape
+    served = M
+    if rows is not None:
+        _chk(rows, "attention rows", torch.int32)
+        served = rows.numel()
     _chk(q, "q", torch.bfloat16)
     _chk(kpool, "key pool", torch.bfloat16)
     _chk(vpool, "value pool", torch.bfloat16, tuple(kpool.shape))
@@ -760,7 +766,7 @@ def attention_decode_tma_split(q, kpool, vpool, block_table, page_size, position
         gate_ptr, gate_ld = c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1]
     num_chunks = int(num_chunks)
     if num_chunks > 1:
-        need = attention_scratch_bytes(M, nh, hd, num_chunks)
+        need = attention_scratch_bytes(served, nh, hd, num_chunks)
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
         _chk(scratch, "attention scratch", torch.uint8)
@@ -770,19 +776,23 @@ def attention_decode_tma_split(q, kpool, vpool, block_table, page_size, position
 
     def work():
         pos = positions.cpu().long()
+        if rows is not None:
+            pos = pos[rows.cpu().long()]
         keys = (pos + 1).clamp(max=int(window)) if window else pos + 1
         if keep:
             keys = keys + (pos + 1 - int(window)).clamp(min=0, max=keep)
         total = int(keys.sum())
-        return total * 2 * nkv * hd * 2 + 2 * M * nh * hd * 2, 4 * nh * hd * total
+        return total * 2 * nkv * hd * 2 + 2 * served * nh * hd * 2, 4 * nh * hd * total
     check(fn("snk_attention_decode_tma_split")(
         _ptr(q), _ptr(kpool), _ptr(vpool), kpool.shape[0], _ptr(block_table), block_table.shape[1], page_size,
-        _ptr(positions), _ptr(row_seg), _ptr(out), _ptr(scratch), M, nh, nkv, hd, int(window or 0), num_chunks,
-        float(scale), keep, _ptr(slopes), _ptr(sink), gate_ptr, gate_ld, _stream()), "attention_decode_tma", work=work)
+        _ptr(positions), _ptr(row_seg), _ptr(rows), _ptr(out), _ptr(scratch), served, nh, nkv, hd, int(window or 0),
+        num_chunks, float(scale), keep, _ptr(slopes), _ptr(sink), gate_ptr, gate_ld, _stream()),
+        "attention_decode_tma", work=work)
     if num_chunks > 1:
-        check(fn("snk_attention_merge_gated")(_ptr(scratch), _ptr(positions), _ptr(out), M, nh, hd, int(window or 0),
-                                              keep, DECODE_MMA_CHUNK, num_chunks, gate_ptr, gate_ld, BF16, _stream()),
-              "attention_merge", work=lambda: (M * nh * (hd + 2) * 4 * num_chunks + M * nh * hd * 2, 0))
+        check(fn("snk_attention_merge_gated")(_ptr(scratch), _ptr(positions), _ptr(out), served, nh, hd,
+                                              int(window or 0), keep, DECODE_MMA_CHUNK, num_chunks, gate_ptr, gate_ld,
+                                              BF16, _ptr(rows), _stream()),
+              "attention_merge", work=lambda: (served * nh * (hd + 2) * 4 * num_chunks + served * nh * hd * 2, 0))
     return out
 
 
@@ -1794,7 +1804,7 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
     if num_chunks > 1:
         check(fn("snk_attention_merge_gated")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, reach, keep,
                                               int(chunk), num_chunks, gate_ptr, gate_ld, code_of(out_dtype),
-                                              _stream()),
+                                              c_void_p(0), _stream()),
               "attention_merge", work=lambda: (M * nq * (dv + 2) * 4 * num_chunks + _nbytes(out), 0))
     return out
 

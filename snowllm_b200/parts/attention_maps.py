@@ -222,13 +222,18 @@ class MapsAttention(Part):
         ctx.tap("attention_q", q)
         if self._prompt_kernel_ok(ctx, q, cache, out_dtype):
             # prompt portions on the tcgen05 kernel; the rows of short segments (decoded tokens beside them) below
-            tc_tiles, _, rows_host = plan.split(ctx, kernels.PREFILL_TC_TILE_ROWS)
+            tc_tiles, rows_dev, rows_host = plan.split(ctx, kernels.PREFILL_TC_TILE_ROWS)
             out = torch.empty(ctx.M, self.nq, self.v_head_dim, dtype=out_dtype, device=q.device)
             kernels.attention_prefill_tc_split(q, kpool, vpool, cache.block_table, cache.page_size, tc_tiles, self.scale,
                                                out, window=self.window, keep=self.keep_first, slopes=self.slopes,
                                                sink=self.sink, gate=proj if self._gate_in_kernel() else None,
                                                gate_col=g_off)
             if not rows_host:
+                ctx.tap("attention_o", out)
+                return proj, out
+            if self._decode_kernel_ok(q, cache, out_dtype):
+                # the rows of short segments (decoded tokens beside the portions) on the TMA decode kernel
+                self._alone(ctx, q, cache, proj, g_off, out, rows_dev, rows_host)
                 ctx.tap("attention_o", out)
                 return proj, out
             tiles = single_row_tiles(ctx, rows_host)
@@ -253,25 +258,31 @@ class MapsAttention(Part):
                 and self.nq // self.num_kv_heads <= kernels.DECODE_MMA_MAX_GROUP
                 and kernels.DECODE_TMA and kernels.decode_tma_page_ok(cache.page_size))
 
+    def _alone(self, ctx, q, cache, proj, g_off, out, rows_dev, rows_host):
+        """Rows that stand alone (all of the step, or ``rows_host``) on the tensor cores, their keys and values by
+        TMA in chunks of 256, written into ``out``."""
+        kpool, vpool = cache.pools
+        chunk = kernels.DECODE_MMA_CHUNK
+        num_chunks = plan.chunks(ctx, self.window, rows_host, chunk, keep=self.keep_first)
+        if self.window:                    # a captured step plans for its longest sequence; a window spans fewer
+            num_chunks = min(num_chunks, (self.window - 1) // chunk + 2 + -(-self.keep_first // chunk))
+        served = ctx.M if rows_host is None else len(rows_host)
+        scratch = ctx.scratch(kernels.attention_scratch_bytes(served, self.nq, self.v_head_dim, num_chunks)) \
+            if num_chunks > 1 else None
+        kernels.attention_decode_tma_split(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
+                                           ctx.row_seg, self.scale, num_chunks, out, window=self.window,
+                                           keep=self.keep_first, slopes=self.slopes, sink=self.sink,
+                                           gate=proj if self._gate_in_kernel() else None, gate_col=g_off,
+                                           scratch=scratch, rows=rows_dev)
+
     def _rows(self, ctx, q, cache, proj, g_off, out_dtype, tiles, tile_rows, out):
         """The kernels of csrc/attention_split.cu: every row of the step (``tiles`` None), or the rows that
         ``tiles`` names, written into ``out``."""
         kpool, vpool = cache.pools
         decode_only = tiles is None and max(ctx.host_seg_len) <= 1
         if decode_only and self._decode_kernel_ok(q, cache, out_dtype):
-            # rows of decoded tokens on the tensor cores, their keys and values by TMA in chunks of 256
-            chunk = kernels.DECODE_MMA_CHUNK
-            num_chunks = plan.chunks(ctx, self.window, None, chunk, keep=self.keep_first)
-            if self.window:                # a captured step plans for its longest sequence; a window spans fewer
-                num_chunks = min(num_chunks, (self.window - 1) // chunk + 2 + -(-self.keep_first // chunk))
-            scratch = ctx.scratch(kernels.attention_scratch_bytes(ctx.M, self.nq, self.v_head_dim, num_chunks)) \
-                if num_chunks > 1 else None
             out = torch.empty(ctx.M, self.nq, self.v_head_dim, dtype=out_dtype, device=q.device)
-            kernels.attention_decode_tma_split(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
-                                               ctx.row_seg, self.scale, num_chunks, out, window=self.window,
-                                               keep=self.keep_first, slopes=self.slopes, sink=self.sink,
-                                               gate=proj if self._gate_in_kernel() else None, gate_col=g_off,
-                                               scratch=scratch)
+            self._alone(ctx, q, cache, proj, g_off, out, None, None)
             ctx.tap("attention_o", out)
             return out
         if tiles is None:
